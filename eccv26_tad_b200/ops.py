@@ -1,0 +1,187 @@
+"""Tensor-level entry points over the C ABI: raw device pointers in, status codes out.
+
+These functions own what the C library does not: allocating outputs and workspaces through
+torch's caching allocator (so they are ordered on the current stream), picking the current
+stream and device, and translating status codes to exceptions.
+"""
+import torch
+
+from . import _lib
+
+_DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dtype_code(t):
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise ValueError(f"unsupported dtype {t.dtype}; expected float32, bfloat16 or float16") from None
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise ValueError("SparseConv2D tensors must live on a CUDA device (there is no CPU path)")
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None and t.numel() > 0 else None
+
+
+def _i32_table(nbr):
+    if nbr.dtype != torch.int32:
+        nbr = nbr.to(torch.int32)
+    return nbr.contiguous()
+
+
+def _workspace(op, n, cin, cout, kk, code, device):
+    nbytes = _lib.load().svtad_workspace_bytes(op, n, cin, cout, kk, code)
+    if nbytes == 0:
+        return None, 0
+    return torch.empty(nbytes, dtype=torch.uint8, device=device), nbytes
+
+
+# ----------------------------------------------------------------------------- table
+def table_init(B, T, h, w, ksize=3, device="cuda"):
+    out = torch.empty((B, T * h * w, ksize * ksize), dtype=torch.int32, device=device)
+    with torch.cuda.device(out.device):
+        _lib.check(_lib.load().svtad_table_init(B, T, h, w, ksize, _ptr(out), _stream()))
+    return out
+
+
+def table_build(scores, k_keep, h, w, ksize=3):
+    """scores float32 [n_seg, seg_len] -> (kept_idx int32 [n_seg, k], table int32 [n_seg*k, ksize^2])."""
+    _require_cuda(scores)
+    if scores.dtype != torch.float32:
+        scores = scores.float()
+    scores = scores.contiguous()
+    n_seg, seg_len = scores.shape
+    kept = torch.empty((n_seg, k_keep), dtype=torch.int32, device=scores.device)
+    table = torch.empty((n_seg * k_keep, ksize * ksize), dtype=torch.int32, device=scores.device)
+    with torch.cuda.device(scores.device):
+        _lib.check(_lib.load().svtad_table_build(_ptr(scores), n_seg, seg_len, k_keep, h, w, ksize,
+                                                 _ptr(kept), _ptr(table), _stream()))
+    return kept, table
+
+
+def topk_select(scores, k_keep):
+    """scores float32 [B, L] -> idx int64 [B, k], ascending (torch.topk + sort with a fixed tie rule)."""
+    _require_cuda(scores)
+    if scores.dtype != torch.float32:
+        scores = scores.float()
+    scores = scores.contiguous()
+    B, L = scores.shape
+    idx = torch.empty((B, k_keep), dtype=torch.int64, device=scores.device)
+    with torch.cuda.device(scores.device):
+        _lib.check(_lib.load().svtad_topk_select(_ptr(scores), B, L, k_keep, _ptr(idx), _stream()))
+    return idx
+
+
+def table_remap(table, idx, scratch=None):
+    """table int32 [B, N_prev, KK], idx int64 [B, N_new] -> int32 [B, N_new, KK]."""
+    _require_cuda(table, idx)
+    table = _i32_table(table)
+    idx = idx.to(torch.int64).contiguous()
+    B, n_prev, kk = table.shape
+    n_new = idx.shape[1]
+    if scratch is None or scratch.numel() < B * n_prev:
+        scratch = torch.empty(B * n_prev, dtype=torch.int32, device=table.device)
+    out = torch.empty((B, n_new, kk), dtype=torch.int32, device=table.device)
+    with torch.cuda.device(table.device):
+        _lib.check(_lib.load().svtad_table_remap(_ptr(table), _ptr(idx), B, n_prev, n_new, kk,
+                                                 _ptr(scratch), _ptr(out), _stream()))
+    return out
+
+
+def table_check(nbr, tokens_per_batch=0, status=None):
+    """Returns a 1-element int32 device tensor: 0 = valid symmetric table (no host sync)."""
+    _require_cuda(nbr)
+    nbr = _i32_table(nbr)
+    kk = nbr.shape[-1]
+    n = nbr.numel() // kk
+    if status is None:
+        status = torch.empty(1, dtype=torch.int32, device=nbr.device)
+    with torch.cuda.device(nbr.device):
+        _lib.check(_lib.load().svtad_table_check(_ptr(nbr), n, kk, tokens_per_batch, _ptr(status), _stream()))
+    return status
+
+
+# ----------------------------------------------------------------------------- conv
+def conv_fwd(x, nbr, weight, bias=None, tokens_per_batch=0):
+    _require_cuda(x, nbr, weight, bias)
+    code = _dtype_code(x)
+    kk, cin, cout = weight.shape
+    x = x.contiguous()
+    weight = weight.contiguous()
+    nbr = _i32_table(nbr)
+    n = x.numel() // cin if cin else 0
+    if weight.dtype != x.dtype or (bias is not None and bias.dtype != x.dtype):
+        raise ValueError("x, weight and bias must share one dtype")
+    out = torch.empty((n, cout), dtype=x.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().svtad_conv_fwd(_ptr(x), _ptr(nbr), _ptr(weight),
+                                              _ptr(bias.contiguous()) if bias is not None else None,
+                                              _ptr(out), n, cin, cout, kk, tokens_per_batch, code,
+                                              None, 0, _stream()))
+    return out
+
+
+def conv_dgrad(gy, nbr, weight, tokens_per_batch=0, table_status=None, assume_symmetric=False):
+    """table_status: tensor from table_check(); assume_symmetric=True skips the scatter-form launch."""
+    _require_cuda(gy, nbr, weight)
+    code = _dtype_code(gy)
+    kk, cin, cout = weight.shape
+    gy = gy.contiguous()
+    weight = weight.contiguous()
+    nbr = _i32_table(nbr)
+    n = gy.numel() // cout
+    if weight.dtype != gy.dtype:
+        raise ValueError("grad_output and weight must share one dtype")
+    gx = torch.empty((n, cin), dtype=gy.dtype, device=gy.device)
+    with torch.cuda.device(gy.device):
+        if assume_symmetric:
+            status, ws, ws_bytes = None, None, 0
+        else:
+            status = table_status if table_status is not None else table_check(nbr, tokens_per_batch)
+            ws, ws_bytes = _workspace(_lib.OP_DGRAD, n, cin, cout, kk, code, gy.device)
+        _lib.check(_lib.load().svtad_conv_dgrad(_ptr(gy), _ptr(nbr), _ptr(weight), _ptr(gx), n, cin, cout,
+                                                kk, tokens_per_batch, code, _ptr(status), _ptr(ws),
+                                                ws_bytes, _stream()))
+    return gx
+
+
+def conv_wgrad(gy, x, nbr, kk, tokens_per_batch=0, with_bias=True):
+    _require_cuda(gy, x, nbr)
+    code = _dtype_code(x)
+    cin = x.shape[-1]
+    cout = gy.shape[-1]
+    gy = gy.contiguous()
+    x = x.contiguous()
+    nbr = _i32_table(nbr)
+    n = x.numel() // cin
+    if gy.dtype != x.dtype:
+        raise ValueError("grad_output and x must share one dtype")
+    gw = torch.empty((kk, cin, cout), dtype=x.dtype, device=x.device)
+    gb = torch.empty((cout,), dtype=x.dtype, device=x.device) if with_bias else None
+    with torch.cuda.device(x.device):
+        ws, ws_bytes = _workspace(_lib.OP_WGRAD, n, cin, cout, kk, code, x.device)
+        _lib.check(_lib.load().svtad_conv_wgrad(_ptr(gy), _ptr(x), _ptr(nbr), _ptr(gw), _ptr(gb), n, cin,
+                                                cout, kk, tokens_per_batch, code, _ptr(ws), ws_bytes,
+                                                _stream()))
+    return gw, gb
+
+
+def device_error():
+    """Reads and clears the device error word (synchronises).  0 = no bounded wait gave up."""
+    import ctypes
+    v = ctypes.c_int32(0)
+    _lib.check(_lib.load().svtad_device_error(ctypes.byref(v)))
+    return v.value
+
+
+def path_for(op, n, cin, cout, kk, dtype):
+    return "tc" if _lib.load().svtad_path_for(op, n, cin, cout, kk, _DTYPES[dtype]) else "simt"

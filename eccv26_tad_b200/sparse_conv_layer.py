@@ -1,0 +1,184 @@
+"""``SparseConv2d`` / ``SparseConv2dFunction`` with the reference's call surface.
+
+Mirrors ``opentad/models/bricks/sparse_conv_layer.py`` of pcr-upm/eccv26_tad: same class names,
+argument order, defaults, parameter names and shapes (``weight (K*K, C_in, C_out)``,
+``bias (C_out)``), same autocast behaviour, same ``ValueError`` for ``C_in % 4 != 0``
+(reference :39-42).  The implementation underneath is ``libsvtad.so`` only; a CPU tensor raises.
+
+Differences, all additive:
+* ``kernel_size`` (keyword-only, default 3) - the reference hard-codes 3x3 (:136, :182);
+* ``chunk_size`` is accepted and ignored - the reference needs it to bound its ``[9, chunk, C]``
+  temporaries (implicit_gemm_v2.cu:361-414); nothing is materialised here;
+* the "indices are local to each batch row" heuristic (reference :170-177, a host sync on every
+  call) is evaluated once per table object and cached, or skipped with ``local_indices=...``;
+* the input gradient uses a gather form that needs a symmetric table (every table built by the
+  backbone's code is).  Arbitrary tables are detected on the device by ``svtad_table_check`` and
+  take the reference's scatter formulation, so results are defined for any table.
+"""
+import math
+
+import torch
+import torch.nn as nn
+from torch.autograd import Function
+from torch.utils.weak import WeakIdKeyDictionary
+
+from . import ops
+
+try:  # torch >= 2.4
+    from torch.amp import custom_bwd as _custom_bwd, custom_fwd as _custom_fwd
+
+    def custom_fwd(fn):
+        return _custom_fwd(fn, device_type="cuda")
+
+    def custom_bwd(fn):
+        return _custom_bwd(fn, device_type="cuda")
+except ImportError:  # pragma: no cover
+    from torch.cuda.amp import custom_bwd, custom_fwd
+
+
+class _PerTableCache:
+    """Facts about a table tensor, valid while the tensor object lives and is not written to."""
+
+    def __init__(self):
+        self._d = WeakIdKeyDictionary()
+
+    def get(self, t, key, make):
+        ent = self._d.get(t)
+        if ent is None or ent[0] != t._version:
+            ent = (t._version, {})
+            self._d[t] = ent
+        if key not in ent[1]:
+            ent[1][key] = make()
+        return ent[1][key]
+
+
+_table_cache = _PerTableCache()
+
+
+def _status_for(nbr, tokens_per_batch):
+    return _table_cache.get(nbr, ("status", tokens_per_batch), lambda: ops.table_check(nbr, tokens_per_batch))
+
+
+class SparseConv2dFunction(Function):
+    """apply(x, neighbor_indices, weight, bias=None, tokens_per_batch=0, chunk_size=0)
+    (reference sparse_conv_layer.py:29-123)."""
+
+    @staticmethod
+    @custom_fwd
+    def forward(ctx, x, neighbor_indices, weight, bias=None, tokens_per_batch=0, chunk_size=0):
+        kk, C_in, C_out = weight.shape
+        if C_in % 4 != 0:
+            raise ValueError(f"C_in ({C_in}) must be divisible by 4 for optimized kernel.")
+        ctx.save_for_backward(x, neighbor_indices, weight, bias)
+        ctx.C_in = C_in
+        ctx.tokens_per_batch = tokens_per_batch
+        ctx.table_status = None
+        if any(ctx.needs_input_grad[:1]):
+            ctx.table_status = _status_for(neighbor_indices, tokens_per_batch)
+        out = ops.conv_fwd(x.reshape(-1, C_in), neighbor_indices.reshape(-1, kk), weight, bias,
+                           tokens_per_batch)
+        return out
+
+    @staticmethod
+    @custom_bwd
+    def backward(ctx, grad_output):
+        x, neighbor_indices, weight, bias = ctx.saved_tensors
+        kk = weight.shape[0]
+        tpb = ctx.tokens_per_batch
+        nbr = neighbor_indices.reshape(-1, kk)
+        grad_input = grad_weight = grad_bias = None
+        if ctx.needs_input_grad[0]:
+            status = ctx.table_status
+            if status is None:
+                status = _status_for(neighbor_indices, tpb)
+            grad_input = ops.conv_dgrad(grad_output, nbr, weight, tpb, table_status=status)
+            if x.dim() == 3:
+                grad_input = grad_input.view(x.shape)
+        need_b = bias is not None and ctx.needs_input_grad[3]
+        if ctx.needs_input_grad[2] or need_b:
+            gw, gb = ops.conv_wgrad(grad_output, x.reshape(-1, ctx.C_in), nbr, kk, tpb, with_bias=need_b)
+            if ctx.needs_input_grad[2]:
+                grad_weight = gw
+            if need_b:
+                grad_bias = gb
+        return grad_input, None, grad_weight, grad_bias, None, None
+
+
+class SparseConv2d(nn.Module):
+    """Drop-in for the reference module (sparse_conv_layer.py:126-211)."""
+
+    def __init__(self, in_channels, out_channels, bias=True, chunk_size=4096, *, kernel_size=3):
+        super().__init__()
+        if kernel_size % 2 != 1:
+            raise ValueError("kernel_size must be odd")
+        self.in_channels = in_channels
+        self.out_channels = out_channels
+        self.chunk_size = chunk_size      # accepted for compatibility; unused
+        self.kernel_size = kernel_size
+        kk = kernel_size * kernel_size
+        self.weight = nn.Parameter(torch.empty(kk, in_channels, out_channels))
+        if bias:
+            self.bias = nn.Parameter(torch.empty(out_channels))
+        else:
+            self.register_parameter("bias", None)
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        # same scheme as the reference (:145-161): Kaiming-uniform(a=sqrt(5)) on (C_out, C_in, K, K),
+        # stored as (K*K, C_in, C_out); bias U(-1/sqrt(fan_in), 1/sqrt(fan_in))
+        k = self.kernel_size
+        temp = torch.empty(self.out_channels, self.in_channels, k, k)
+        nn.init.kaiming_uniform_(temp, a=math.sqrt(5))
+        with torch.no_grad():
+            self.weight.copy_(temp.view(self.out_channels, self.in_channels, k * k).permute(2, 1, 0))
+        if self.bias is not None:
+            fan_in = self.in_channels * k * k
+            bound = 1 / math.sqrt(fan_in)
+            nn.init.uniform_(self.bias, -bound, bound)
+
+    def forward(self, x, neighbor_indices, local_indices=None):
+        kk = self.kernel_size * self.kernel_size
+        is_batched = x.dim() == 3
+        tokens_per_batch = 0
+        if is_batched:
+            B, N, C = x.shape
+            if local_indices is None:
+                # reference heuristic (:170-177): indices are local iff max < N; cached per table object
+                if neighbor_indices.numel() > 0:
+                    local_indices = _table_cache.get(
+                        neighbor_indices, ("local", N), lambda: bool(neighbor_indices.max() < N))
+                else:
+                    local_indices = False
+            if local_indices:
+                tokens_per_batch = N
+            x = x.reshape(-1, C)
+        table = neighbor_indices
+        if table.dtype != torch.int32:
+            table = _table_cache.get(neighbor_indices, "int32", lambda: neighbor_indices.to(torch.int32))
+        if table.dim() == 3:
+            table = _table_cache.get(table, "flat", lambda: table.reshape(-1, kk)) if table.is_contiguous() \
+                else table.reshape(-1, kk)
+
+        weight = self.weight
+        bias = self.bias
+        if torch.is_autocast_enabled():
+            target_dtype = torch.get_autocast_dtype("cuda")
+            if x.dtype != target_dtype:
+                x = x.to(target_dtype)
+            if weight.dtype != target_dtype:
+                weight = weight.to(target_dtype)
+            if bias is not None and bias.dtype != target_dtype:
+                bias = bias.to(target_dtype)
+        elif x.dtype != weight.dtype:
+            weight = weight.to(x.dtype)
+            if bias is not None:
+                bias = bias.to(x.dtype)
+
+        output = SparseConv2dFunction.apply(x, table, weight, bias, tokens_per_batch, self.chunk_size)
+        if is_batched:
+            output = output.view(B, N, -1)
+        return output
+
+    def extra_repr(self):
+        return (f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}, "
+                f"bias={self.bias is not None}")

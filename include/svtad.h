@@ -1,0 +1,154 @@
+/*
+ * svtad.h - C ABI of libsvtad.so: SparseConv2D (SV-TAD) for NVIDIA B200 (sm_100a).
+ *
+ * This is the whole drop-in boundary of the library.  Every function takes plain device
+ * pointers and sizes, launches on the CUDA stream handed in, never allocates and never
+ * synchronises the host; inputs, outputs and workspaces belong to the caller.  Every
+ * function returns 0 on success or one of the SVTAD_ERR_* codes below, in which case
+ * svtad_last_error_string() describes the problem (thread-local).  Bad arguments are
+ * rejected on the host; nothing on the device asserts or traps.
+ *
+ * Conventions shared by all entry points
+ *   nbr      int32 [n, kk]   neighbor table; column k = (dy+r)*K + (dx+r), r = K/2, dy outer;
+ *                            entry = row index of that neighbor in the SAME [n, C] tensor, or -1
+ *   w        [kk, cin, cout] weight, pre-permuted layout of the reference module
+ *   dtype    SVTAD_F32 / SVTAD_BF16 / SVTAD_F16 - type of every floating tensor of the call;
+ *            products and sums are always fp32, one rounding at the end
+ *   tokens_per_batch  > 0: table entries are local to blocks of that many rows and
+ *            off(i) = (i / tokens_per_batch) * tokens_per_batch is added per row; 0: global
+ *   stream   a cudaStream_t (passed as void* so that C callers need no CUDA headers)
+ *
+ * Reference interfaces replaced (paths inside pcr-upm/eccv26_tad):
+ *   the pybind module opentad_sparse_ops, opentad/models/bricks/2d_sparse_v3_bind.cpp:8-14,
+ *   and the torch-op table code of opentad/models/backbones/vit_sparse_adapter_poguise.py.
+ */
+#ifndef SVTAD_H_
+#define SVTAD_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SVTAD_OK 0
+#define SVTAD_ERR_ARG 1          /* null pointer, negative size, misaligned pointer ...        */
+#define SVTAD_ERR_UNSUPPORTED 2  /* shape / dtype outside what the kernels implement            */
+#define SVTAD_ERR_WORKSPACE 3    /* workspace smaller than svtad_workspace_bytes() says         */
+#define SVTAD_ERR_CUDA 4         /* a CUDA runtime call or a kernel launch reported an error    */
+
+#define SVTAD_F32 0
+#define SVTAD_BF16 1
+#define SVTAD_F16 2
+
+#define SVTAD_OP_FWD 0
+#define SVTAD_OP_DGRAD 1
+#define SVTAD_OP_WGRAD 2
+
+/* Bits of the device status word written by svtad_table_check(). */
+#define SVTAD_TABLE_OUT_OF_RANGE 1
+#define SVTAD_TABLE_ASYMMETRIC 2
+
+int svtad_version(void);
+
+/* Text of the last error raised on the calling thread ("" if none). */
+const char* svtad_last_error_string(void);
+
+/*
+ * Full-grid table: table[b, t*h*w + y*w + x, k] = global index of (b, t, y+dy, x+dx) or -1
+ * outside the h x w grid.  table: int32 [B, T*h*w, ksize*ksize].
+ * Replaces get_initial_neighbor_indices, vit_sparse_adapter_poguise.py:1623-1670.
+ */
+int svtad_table_init(int B, int T, int h, int w, int ksize, int32_t* table, void* stream);
+
+/*
+ * Fused selection + table for one pruning round that starts from the full grid.
+ * scores: float32 [n_seg, seg_len], seg_len a multiple of h*w (a segment is a slice or a clip).
+ * Keeps the k_keep largest scores of every segment (ties: lower index wins; NaN is largest),
+ * writes kept_idx int32 [n_seg, k_keep] (ascending positions inside the segment) and
+ * table int32 [n_seg*k_keep, ksize*ksize] (global indices seg*k_keep + rank, or -1).
+ * Replaces torch.topk + sort (vit_sparse_adapter_poguise.py:785-787) followed by the
+ * gather + remap of :913-977 applied to the table of :1623-1670.
+ */
+int svtad_table_build(const float* scores, int n_seg, int seg_len, int k_keep, int h, int w,
+                      int ksize, int32_t* kept_idx, int32_t* table, void* stream);
+
+/*
+ * Selection alone: idx int64 [n_seg, k_keep], ascending, same tie / NaN rule as above.
+ * Replaces torch.topk + sort, vit_sparse_adapter_poguise.py:785-787.
+ */
+int svtad_topk_select(const float* scores, int n_seg, int seg_len, int k_keep, int64_t* idx,
+                      void* stream);
+
+/*
+ * One pruning round on an existing table.  table_in int32 [B, n_prev, kk] (global over
+ * B*n_prev), idx int64 [B, n_new] kept positions per batch row, scratch int32 [B*n_prev]
+ * (overwritten), table_out int32 [B, n_new, kk] (global over B*n_new).
+ * Replaces the gather + remap in Block._inner_forward, vit_sparse_adapter_poguise.py:913-977;
+ * scratch is that code's global_mapping_buffer (:1713-1717).
+ */
+int svtad_table_remap(const int32_t* table_in, const int64_t* idx, int B, int n_prev, int n_new,
+                      int kk, int32_t* scratch, int32_t* table_out, void* stream);
+
+/*
+ * Validates a table on the device: ORs SVTAD_TABLE_OUT_OF_RANGE / SVTAD_TABLE_ASYMMETRIC into
+ * status[0] (int32, device memory, cleared by this call first).  "Symmetric" means
+ * nbr[nbr[i,k]+off, kk-1-k]+off == i for every valid entry, which every table produced by the
+ * functions above satisfies.  Counterpart of the debug validator
+ * opentad/models/backbones/internvideo_next.py:41-70, but it reports instead of asserting.
+ */
+int svtad_table_check(const int32_t* nbr, int64_t n, int kk, int tokens_per_batch,
+                      int32_t* status, void* stream);
+
+/* Workspace size (bytes) that the given op needs for the given problem (0 for the forward). */
+size_t svtad_workspace_bytes(int op, int64_t n, int cin, int cout, int kk, int dtype);
+
+/*
+ * y[i,co] = bias[co] + sum_k sum_ci x[nbr[i,k]+off(i), ci] * w[k,ci,co]; bias may be NULL.
+ * Replaces fwd, implicit_gemm_fwd_v2 and implicit_gemm_fwd_v2_chunked
+ * (2d_sparse_v3.cu:751-822, implicit_gemm_v2.cu:197-300, :306-417).
+ */
+int svtad_conv_fwd(const void* x, const int32_t* nbr, const void* w, const void* bias, void* y,
+                   int64_t n, int cin, int cout, int kk, int tokens_per_batch, int dtype,
+                   void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * gx[j,ci] = sum over (i,k) with nbr[i,k]+off(i)==j of sum_co gy[i,co] * w[k,ci,co].
+ * table_status: NULL when the caller guarantees a symmetric table (the gather form is used);
+ * otherwise the device word written by svtad_table_check() - the kernels read it on the
+ * device and take the scatter form (fp32 atomics into the workspace) for asymmetric tables.
+ * Replaces bwd_in, 2d_sparse_v3.cu:824-835 (kernel :656-709).
+ */
+int svtad_conv_dgrad(const void* gy, const int32_t* nbr, const void* w, void* gx, int64_t n,
+                     int cin, int cout, int kk, int tokens_per_batch, int dtype,
+                     const int32_t* table_status, void* workspace, size_t workspace_bytes,
+                     void* stream);
+
+/*
+ * gw[k,ci,co] = sum_i [nbr[i,k]!=-1] x[nbr[i,k]+off(i), ci] * gy[i,co]; gb[co] = sum_i gy[i,co]
+ * (gb may be NULL).  Deterministic: split over tokens into the workspace, then a fixed-order
+ * reduction.  Replaces bwd_w, 2d_sparse_v3.cu:837-850 (kernel :714-745) and the bias-grad
+ * reduction sparse_conv_layer.py:119-121.
+ */
+int svtad_conv_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw, void* gb,
+                     int64_t n, int cin, int cout, int kk, int tokens_per_batch, int dtype,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Reads (and clears) the device-side error word of the current device: non-zero means a bounded
+ * wait inside a tensor-core kernel gave up and that launch's output is invalid.  Synchronises
+ * the device.  No reference counterpart.
+ */
+int svtad_device_error(int32_t* code_out);
+
+/*
+ * Which implementation the given problem dispatches to: 0 = CUDA-core (SIMT) kernels,
+ * 1 = tcgen05 tensor-core kernels.  Honours the SVTAD_FORCE_PATH=simt|tc environment override.
+ */
+int svtad_path_for(int op, int64_t n, int cin, int cout, int kk, int dtype);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SVTAD_H_ */

@@ -1,0 +1,239 @@
+"""GPU tier: SparseConv2D forward / dgrad / wgrad through the C ABI against the CPU oracle.
+
+Error metric everywhere: max|a - ref| / max|ref| per tensor (``oracle.conv.rel_err``).
+Tolerances: fp32 1e-5, bf16 / fp16 outputs and gradients 2e-2.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import conv as oconv
+from oracle import table as otab
+from tests.helpers import BASE_SEED, f32np, make_conv_inputs, make_table
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-5, torch.bfloat16: 2e-2, torch.float16: 2e-2}
+
+
+def _ops():
+    from eccv26_tad_b200 import ops
+    return ops
+
+
+@pytest.fixture(autouse=True)
+def _no_forced_path(monkeypatch):
+    monkeypatch.delenv("SVTAD_FORCE_PATH", raising=False)
+    monkeypatch.delenv("SVTAD_TC_BN", raising=False)
+    yield
+    assert _ops().device_error() == 0, "a bounded wait inside a tensor-core kernel gave up"
+
+
+def _run_all(table, x, w, b, gy, tpb=0, sym=None):
+    ops = _ops()
+    kk = w.shape[0]
+    tc, xc, wc, bc, gc = (t.cuda() for t in (table, x, w, b, gy))
+    y = ops.conv_fwd(xc, tc, wc, bc, tpb)
+    gx = ops.conv_dgrad(gc, tc, wc, tpb, assume_symmetric=bool(sym)) if sym is not None else ops.conv_dgrad(gc, tc, wc, tpb)
+    gw, gb = ops.conv_wgrad(gc, xc, tc, kk, tpb)
+    torch.cuda.synchronize()
+    return y, gx, gw, gb
+
+
+def _check_all(table, x, w, b, gy, outs, tol, tpb=0):
+    y, gx, gw, gb = outs
+    tn = table.numpy()
+    xf, wf, bf, gf = (f32np(t) for t in (x, w, b, gy))
+    kk = w.shape[0]
+    errs = {
+        "y": oconv.rel_err(f32np(y), oconv.fwd(xf, tn, wf, bf, tpb)),
+        "gx": oconv.rel_err(f32np(gx), oconv.dgrad(gf, tn, wf, tpb)),
+    }
+    egw, egb = oconv.wgrad(gf, xf, tn, kk, tpb)
+    errs["gw"] = oconv.rel_err(f32np(gw), egw)
+    errs["gb"] = oconv.rel_err(f32np(gb), egb)
+    for k, v in errs.items():
+        assert v < tol, f"{k}: rel err {v:.3e} >= {tol}"
+    assert y.dtype == x.dtype and gx.dtype == gy.dtype and gw.dtype == x.dtype and gb.dtype == x.dtype
+    return errs
+
+
+def test_config1_fp32_forward_and_backward():
+    """fp32, batch 1, T=8, 14x14, C=192, keep 50% by seeded random choice (98 tokens per slice)."""
+    rng = np.random.default_rng(BASE_SEED + 1)
+    scores = rng.standard_normal((8, 196)).astype(np.float32)      # top-k of iid scores == uniform subset
+    kept, table = otab.build_table(scores, 98, 14, 14, 3)
+    table = torch.from_numpy(table)
+    assert table.shape == (784, 9)
+    x, w, b, gy = make_conv_inputs(784, 192, 192, 3, torch.float32, BASE_SEED + 1)
+    assert _ops().path_for(0, 784, 192, 192, 9, torch.float32) == "simt"
+    outs = _run_all(table, x, w, b, gy)
+    _check_all(table, x, w, b, gy, outs, 1e-5)
+
+
+@pytest.mark.parametrize("keep", [0.10, 0.30, 0.55])
+@pytest.mark.parametrize("path", ["tc", "simt"])
+def test_config2_bf16_fwd_bwd_full_size(keep, path, monkeypatch):
+    """bf16, batch 2, T=80 (160 slices), 14x14, C=192, keep sweep; both implementations."""
+    monkeypatch.setenv("SVTAD_FORCE_PATH", path)
+    _, _, table = make_table(2, 80, 14, 14, keep, 3, BASE_SEED + 2)
+    n = table.shape[0]
+    assert n == {0.10: 3200, 0.30: 9440, 0.55: 17280}[keep]
+    x, w, b, gy = make_conv_inputs(n, 192, 192, 3, torch.bfloat16, BASE_SEED + 2, bias="random")
+    outs = _run_all(table, x, w, b, gy)
+    _check_all(table, x, w, b, gy, outs, 2e-2)
+
+
+@pytest.mark.parametrize("bn", ["64", "192"])
+def test_tc_column_block_variants(bn, monkeypatch):
+    monkeypatch.setenv("SVTAD_FORCE_PATH", "tc")
+    monkeypatch.setenv("SVTAD_TC_BN", bn)
+    _, _, table = make_table(1, 10, 14, 14, 0.3, 3, 99)
+    n = table.shape[0]
+    x, w, b, gy = make_conv_inputs(n, 192, 192, 3, torch.bfloat16, 99, bias="random")
+    outs = _run_all(table, x, w, b, gy)
+    _check_all(table, x, w, b, gy, outs, 2e-2)
+
+
+def test_tc_and_simt_agree_tightly(monkeypatch):
+    """Same bf16 inputs, fp32 accumulation on both paths: outputs differ by rounding only."""
+    _, _, table = make_table(2, 8, 14, 14, 0.3, 3, 5)
+    n = table.shape[0]
+    x, w, b, gy = make_conv_inputs(n, 192, 192, 3, torch.bfloat16, 5, bias="random")
+    monkeypatch.setenv("SVTAD_FORCE_PATH", "tc")
+    a = _run_all(table, x, w, b, gy)
+    monkeypatch.setenv("SVTAD_FORCE_PATH", "simt")
+    c = _run_all(table, x, w, b, gy)
+    for u, v in zip(a, c):
+        assert oconv.rel_err(f32np(u), f32np(v)) < 8e-3      # one bf16 ulp is 2^-8 = 3.9e-3
+
+
+@pytest.mark.parametrize("C,ks", [(256, 3), (256, 5), (768, 3), (1024, 3)])
+def test_config3_large_channels_reduced_rows(C, ks):
+    """Large-channel regime at reduced row count (batch 1, T=6) so the CPU oracle finishes in seconds."""
+    _, _, table = make_table(1, 6, 14, 14, 0.3, ks, BASE_SEED + 3)
+    n = table.shape[0]
+    x, w, b, gy = make_conv_inputs(n, C, C, ks, torch.bfloat16, BASE_SEED + 3, bias="random")
+    assert _ops().path_for(0, n, C, C, ks * ks, torch.bfloat16) == "tc"
+    outs = _run_all(table, x, w, b, gy)
+    _check_all(table, x, w, b, gy, outs, 2e-2)
+
+
+def test_config3_full_size_adjoint_identities():
+    """Full size (batch 4, T=80, keep 30%, C=256): <fwd(x), gy> == <x, dgrad(gy)> == <W, wgrad>."""
+    ops = _ops()
+    _, _, table = make_table(4, 80, 14, 14, 0.3, 3, BASE_SEED + 3)
+    n = table.shape[0]
+    assert n == 18880
+    x, w, b, gy = make_conv_inputs(n, 256, 256, 3, torch.bfloat16, BASE_SEED + 3)
+    tc, xc, wc, gc = table.cuda(), x.cuda(), w.cuda(), gy.cuda()
+    y = ops.conv_fwd(xc, tc, wc, None)
+    gx = ops.conv_dgrad(gc, tc, wc)
+    gw, gb = ops.conv_wgrad(gc, xc, tc, 9)
+    lhs = (y.double() * gc.double()).sum().item()
+    mid = (gx.double() * xc.double()).sum().item()
+    rhs = (gw.double() * wc.double()).sum().item()
+    scale = (y.double().abs() * gc.double().abs()).sum().item()
+    assert abs(lhs - mid) < 2e-2 * scale and abs(lhs - rhs) < 2e-2 * scale
+    assert oconv.rel_err(f32np(gb), f32np(gy).astype(np.float64).sum(0)) < 2e-2
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_golden_dense_identity(dtype, golden_dir):
+    """scatter -> conv2d -> gather golden vectors (includes 5x5 and 100% keep)."""
+    g = np.load(os.path.join(golden_dir, "conv_dense_identity.npz"))
+    for name in ("k3", "k3_full", "k5", "k3_c16"):
+        table = torch.from_numpy(g[name + "_table"])
+        x, w, b, gy = (torch.from_numpy(g[f"{name}_{q}"]).to(dtype) for q in ("x", "w", "bias", "gy"))
+        outs = _run_all(table, x, w, b, gy)
+        if dtype == torch.float32:
+            y, gx, gw, gb = outs
+            assert oconv.rel_err(f32np(y), g[name + "_y"]) < 1e-5
+            assert oconv.rel_err(f32np(gx), g[name + "_gx"]) < 1e-5
+            assert oconv.rel_err(f32np(gw), g[name + "_gw"]) < 1e-5
+            assert oconv.rel_err(f32np(gb), g[name + "_gb"]) < 1e-5
+        else:
+            _check_all(table, x, w, b, gy, outs, 2e-2)
+
+
+@pytest.mark.parametrize("dtype,C", [(torch.float32, 64), (torch.bfloat16, 64), (torch.bfloat16, 192), (torch.float32, 40)])
+def test_tokens_per_batch_local_indices(dtype, C):
+    """Local tables + tokens_per_batch == global tables (tokens_per_batch a multiple of 32)."""
+    ops = _ops()
+    _, _, tab1 = make_table(1, 2, 8, 8, 0.5, 3, 11)          # 64 tokens, local to one batch row
+    tpb = tab1.shape[0]
+    assert tpb % 32 == 0
+    B = 5
+    local = tab1.repeat(B, 1)
+    glob = torch.cat([torch.where(tab1 >= 0, tab1 + b * tpb, tab1) for b in range(B)])
+    x, w, b, gy = make_conv_inputs(B * tpb, C, C, 3, dtype, 11, bias="random")
+    a = _run_all(local, x, w, b, gy, tpb=tpb)
+    c = _run_all(glob, x, w, b, gy, tpb=0)
+    for u, v in zip(a, c):
+        assert torch.equal(u, v)
+    _check_all(local, x, w, b, gy, a, TOL[dtype], tpb=tpb)
+
+
+@pytest.mark.parametrize("dtype,C", [(torch.float32, 32), (torch.bfloat16, 128)])
+def test_asymmetric_table_takes_scatter_form(dtype, C):
+    """Arbitrary (non-geometric) tables: dgrad must still be the adjoint of the forward."""
+    rng = np.random.default_rng(21)
+    n = 300
+    table = torch.from_numpy(rng.integers(-1, n, size=(n, 9)).astype(np.int32))
+    x, w, b, gy = make_conv_inputs(n, C, C, 3, dtype, 21, bias="random")
+    outs = _run_all(table, x, w, b, gy)
+    _check_all(table, x, w, b, gy, outs, TOL[dtype])
+
+
+@pytest.mark.parametrize("n", [1, 31, 129, 1000])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_ragged_row_counts_and_odd_widths(n, dtype):
+    rng = np.random.default_rng(n)
+    # a geometric table on a ragged number of rows: 1-D chain (left / centre / right taps only)
+    table = -np.ones((n, 9), dtype=np.int32)
+    table[:, 4] = np.arange(n)
+    table[1:, 3] = np.arange(n - 1)
+    table[:-1, 5] = np.arange(1, n)
+    table = torch.from_numpy(table)
+    for cin, cout in [(64, 64), (8, 20), (192, 64)]:
+        x, w, b, gy = make_conv_inputs(n, cin, cout, 3, dtype, n, bias="random")
+        outs = _run_all(table, x, w, b, gy)
+        _check_all(table, x, w, b, gy, outs, TOL[dtype])
+
+
+def test_empty_input_and_all_pruned_rows():
+    ops = _ops()
+    w = torch.randn(9, 64, 64).cuda().bfloat16()
+    y = ops.conv_fwd(torch.empty(0, 64).cuda().bfloat16(), torch.empty(0, 9, dtype=torch.int32).cuda(), w, None)
+    assert y.shape == (0, 64)
+    gw, gb = ops.conv_wgrad(torch.empty(0, 64).cuda().bfloat16(), torch.empty(0, 64).cuda().bfloat16(),
+                            torch.empty(0, 9, dtype=torch.int32).cuda(), 9)
+    assert float(gw.abs().sum()) == 0 and float(gb.abs().sum()) == 0
+    # rows whose every neighbour (centre included) is -1 produce bias only
+    n = 200
+    table = -torch.ones(n, 9, dtype=torch.int32)
+    x, w, b, gy = make_conv_inputs(n, 64, 64, 3, torch.bfloat16, 1, bias="random")
+    y = ops.conv_fwd(x.cuda(), table.cuda(), w.cuda(), b.cuda())
+    assert torch.equal(y.cpu(), b.expand(n, -1).contiguous())
+
+
+def test_determinism_of_backward():
+    _, _, table = make_table(2, 20, 14, 14, 0.3, 3, 8)
+    n = table.shape[0]
+    x, w, b, gy = make_conv_inputs(n, 192, 192, 3, torch.bfloat16, 8)
+    a = _run_all(table, x, w, b, gy)
+    c = _run_all(table, x, w, b, gy)
+    for u, v in zip(a, c):
+        assert torch.equal(u, v)
+
+
+def test_errors_are_python_exceptions():
+    ops = _ops()
+    w = torch.randn(9, 6, 8).cuda()
+    with pytest.raises(ValueError, match="divisible by 4"):
+        ops.conv_fwd(torch.randn(4, 6).cuda(), torch.zeros(4, 9, dtype=torch.int32).cuda(), w, None)
+    with pytest.raises(ValueError):
+        ops.conv_fwd(torch.randn(4, 8).cuda().double(), torch.zeros(4, 9, dtype=torch.int32).cuda(),
+                     torch.randn(9, 8, 8).cuda().double(), None)

@@ -1,0 +1,121 @@
+"""GPU tier: the reference-facing Python surface (module, autograd Function, pybind-module shim)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import conv as oconv
+from tests.helpers import f32np, make_conv_inputs, make_table
+
+pytestmark = pytest.mark.gpu
+
+
+def _oracle_grads(table, x, w, b, gy, tpb=0):
+    tn = table.numpy()
+    xf, wf, bf, gf = (f32np(t) for t in (x, w, b, gy))
+    y = oconv.fwd(xf, tn, wf, bf, tpb)
+    gx = oconv.dgrad(gf, tn, wf, tpb)
+    gw, gb = oconv.wgrad(gf, xf, tn, w.shape[0], tpb)
+    return y, gx, gw, gb
+
+
+def test_module_fp32_autograd_matches_oracle():
+    from eccv26_tad_b200 import SparseConv2d
+    _, _, table = make_table(1, 4, 14, 14, 0.5, 3, 31)
+    n = table.shape[0]
+    x, w, b, gy = make_conv_inputs(n, 64, 96, 3, torch.float32, 31, bias="random")
+    m = SparseConv2d(64, 96).cuda()
+    with torch.no_grad():
+        m.weight.copy_(w); m.bias.copy_(b)
+    xc = x.cuda().requires_grad_(True)
+    y = m(xc, table.cuda())
+    y.backward(gy.cuda())
+    ey, egx, egw, egb = _oracle_grads(table, x, w, b, gy)
+    assert oconv.rel_err(f32np(y), ey) < 1e-5
+    assert oconv.rel_err(f32np(xc.grad), egx) < 1e-5
+    assert oconv.rel_err(f32np(m.weight.grad), egw) < 1e-5
+    assert oconv.rel_err(f32np(m.bias.grad), egb) < 1e-5
+
+
+def test_module_autocast_bf16_batched_local_and_global_indices():
+    """3-D input under bf16 autocast, fp32 master parameters (the reference's training setting)."""
+    from eccv26_tad_b200 import SparseConv2d
+    _, _, tab1 = make_table(1, 4, 14, 14, 0.3, 3, 32)
+    N = tab1.shape[0]
+    B = 3
+    x, w, b, gy = make_conv_inputs(B * N, 192, 192, 3, torch.float32, 32, bias="random")
+    m = SparseConv2d(192, 192).cuda()
+    with torch.no_grad():
+        m.weight.copy_(w); m.bias.copy_(b)
+    local = tab1.unsqueeze(0).repeat(B, 1, 1).cuda()
+    glob = torch.stack([torch.where(tab1 >= 0, tab1 + i * N, tab1) for i in range(B)]).cuda()
+    # the oracle sees the bf16-rounded operands the autocast path produces
+    xb, wb, bb, gb_ = (t.bfloat16() for t in (x, w, b, gy))
+    ey, egx, egw, egb = _oracle_grads(glob.reshape(-1, 9).cpu(), xb, wb, bb, gb_)
+    for table in (local, glob.long()):           # int64 tables are accepted like in the reference
+        m.zero_grad()
+        xc = x.view(B, N, 192).cuda().requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = m(xc, table)
+        assert y.shape == (B, N, 192) and y.dtype == torch.bfloat16
+        y.backward(gy.view(B, N, 192).cuda().bfloat16())
+        assert xc.grad.shape == xc.shape and xc.grad.dtype == torch.float32
+        assert m.weight.grad.dtype == torch.float32
+        assert oconv.rel_err(f32np(y).reshape(-1, 192), ey) < 2e-2
+        assert oconv.rel_err(f32np(xc.grad).reshape(-1, 192), egx) < 2e-2
+        assert oconv.rel_err(f32np(m.weight.grad), egw) < 2e-2
+        assert oconv.rel_err(f32np(m.bias.grad), egb) < 2e-2
+
+
+def test_function_apply_signature_and_partial_grads():
+    from eccv26_tad_b200 import SparseConv2dFunction
+    _, _, table = make_table(1, 2, 14, 14, 0.5, 3, 33)
+    n = table.shape[0]
+    x, w, b, gy = make_conv_inputs(n, 64, 64, 3, torch.bfloat16, 33, bias="random")
+    xc = x.cuda()                                   # no grad for x
+    wc = w.cuda().requires_grad_(True)
+    y = SparseConv2dFunction.apply(xc, table.cuda(), wc, None, 0, 4096)
+    y.backward(gy.cuda())
+    assert wc.grad is not None and wc.grad.shape == wc.shape
+    ey, _, egw, _ = _oracle_grads(table, x, w, torch.zeros(64), gy)
+    assert oconv.rel_err(f32np(y), ey) < 2e-2
+    assert oconv.rel_err(f32np(wc.grad), egw) < 2e-2
+    with pytest.raises(ValueError, match="divisible by 4"):
+        SparseConv2dFunction.apply(torch.randn(4, 6).cuda(), torch.zeros(4, 9, dtype=torch.int32).cuda(),
+                                   torch.randn(9, 6, 8).cuda())
+
+
+def test_pybind_module_shim_signatures():
+    from eccv26_tad_b200 import opentad_sparse_ops as lib
+    _, _, table = make_table(1, 3, 14, 14, 0.5, 3, 34)
+    n = table.shape[0]
+    x, w, b, gy = make_conv_inputs(n, 128, 128, 3, torch.bfloat16, 34, bias="random")
+    tc, xc, wc, bc, gc = (t.cuda() for t in (table, x, w, b, gy))
+    ey, egx, egw, _ = _oracle_grads(table, x, w, b, gy)
+    y0, _, _, _ = _oracle_grads(table, x, w, torch.zeros(128), gy)
+    assert oconv.rel_err(f32np(lib.fwd(xc, tc, wc, 128, 0)), y0) < 2e-2
+    assert oconv.rel_err(f32np(lib.implicit_gemm_fwd_v2(xc, tc, wc, bc, 0)), ey) < 2e-2
+    assert oconv.rel_err(f32np(lib.implicit_gemm_fwd_v2(xc, tc, wc, torch.Tensor(), 0)), y0) < 2e-2
+    assert oconv.rel_err(f32np(lib.implicit_gemm_fwd_v2_chunked(xc, tc, wc, bc, 0, 4096)), ey) < 2e-2
+    assert oconv.rel_err(f32np(lib.bwd_in(gc, tc, wc, n, 128, 0)), egx) < 2e-2
+    assert oconv.rel_err(f32np(lib.bwd_w(gc, xc, tc, 128, 0)), egw) < 2e-2
+    import sys
+    lib.install()
+    assert sys.modules["opentad_sparse_ops"].fwd is lib.fwd
+    del sys.modules["opentad_sparse_ops"]
+
+
+def test_kernel_size_5_module():
+    from eccv26_tad_b200 import SparseConv2d
+    _, _, table = make_table(1, 3, 14, 14, 0.4, 5, 35)
+    n = table.shape[0]
+    x, w, b, gy = make_conv_inputs(n, 64, 64, 5, torch.bfloat16, 35, bias="random")
+    m = SparseConv2d(64, 64, kernel_size=5).cuda().bfloat16()
+    with torch.no_grad():
+        m.weight.copy_(w); m.bias.copy_(b)
+    xc = x.cuda().requires_grad_(True)
+    y = m(xc, table.cuda())
+    y.backward(gy.cuda())
+    ey, egx, egw, egb = _oracle_grads(table, x, w, b, gy)
+    assert oconv.rel_err(f32np(y), ey) < 2e-2
+    assert oconv.rel_err(f32np(xc.grad), egx) < 2e-2
+    assert oconv.rel_err(f32np(m.weight.grad), egw) < 2e-2

@@ -1,0 +1,89 @@
+"""CPU tier: the C-ABI library loads, exports every symbol the header declares, and rejects
+bad arguments on the host (no kernel is launched by anything in this file)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from eccv26_tad_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "svtad.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(svtad_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported_and_bound():
+    names = _declared_symbols()
+    assert len(names) >= 12
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/svtad.h but not exported"
+        assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
+    assert sorted(_lib.SIGNATURES) == names
+
+
+def test_version_and_error_string():
+    lib = _lib.load()
+    assert lib.svtad_version() >= 100
+    assert isinstance(_lib.last_error(), str)
+
+
+def test_host_side_validation_returns_codes():
+    lib = _lib.load()
+    # C_in % 4 != 0 -> same complaint as the reference wrapper (sparse_conv_layer.py:39-42)
+    rc = lib.svtad_conv_fwd(None, None, None, None, None, 10, 6, 8, 9, 0, _lib.F32, None, 0, None)
+    assert rc == _lib.ERR_UNSUPPORTED and "divisible by 4" in _lib.last_error()
+    rc = lib.svtad_conv_fwd(None, None, None, None, None, -1, 8, 8, 9, 0, _lib.F32, None, 0, None)
+    assert rc == _lib.ERR_ARG
+    rc = lib.svtad_conv_fwd(None, None, None, None, None, 4, 8, 8, 9, 0, 7, None, 0, None)
+    assert rc == _lib.ERR_ARG and "dtype" in _lib.last_error()
+    rc = lib.svtad_conv_fwd(None, None, None, None, None, 4, 8, 8, 9, 0, _lib.F32, None, 0, None)
+    assert rc == _lib.ERR_ARG and "null" in _lib.last_error()
+    rc = lib.svtad_conv_wgrad(None, None, None, None, None, 4, 8, 8, 9, 0, _lib.F32, None, 0, None)
+    assert rc == _lib.ERR_ARG
+    rc = lib.svtad_table_build(None, 4, 196, 300, 14, 14, 3, None, None, None)
+    assert rc == _lib.ERR_ARG and "k_keep" in _lib.last_error()
+    rc = lib.svtad_table_build(None, 4, 200, 20, 14, 14, 3, None, None, None)
+    assert rc == _lib.ERR_ARG
+    rc = lib.svtad_table_init(1, 1, 14, 14, 4, None, None)
+    assert rc == _lib.ERR_ARG and "odd" in _lib.last_error()
+    with pytest.raises(ValueError):
+        _lib.check(rc)
+    # empty problems are fine and touch nothing
+    assert lib.svtad_conv_fwd(None, None, None, None, None, 0, 8, 8, 9, 0, _lib.F32, None, 0, None) == 0
+    assert lib.svtad_table_init(0, 8, 14, 14, 3, None, None) == 0
+
+
+def test_workspace_and_path_queries():
+    lib = _lib.load()
+    assert lib.svtad_workspace_bytes(_lib.OP_FWD, 9440, 192, 192, 9, _lib.BF16) == 0
+    w = lib.svtad_workspace_bytes(_lib.OP_WGRAD, 9440, 192, 192, 9, _lib.BF16)
+    assert w >= 9 * 192 * 192 * 4
+    assert lib.svtad_workspace_bytes(_lib.OP_DGRAD, 100, 192, 192, 9, _lib.BF16) >= 100 * 192 * 4
+    assert lib.svtad_path_for(_lib.OP_FWD, 9440, 192, 192, 9, _lib.BF16) == 1
+    assert lib.svtad_path_for(_lib.OP_FWD, 784, 192, 192, 9, _lib.F32) == 0
+    assert lib.svtad_path_for(_lib.OP_FWD, 784, 48, 48, 9, _lib.BF16) == 0
+
+
+def test_module_surface_matches_reference():
+    import inspect
+    import torch
+    from eccv26_tad_b200 import SparseConv2d, SparseConv2dFunction
+    m = SparseConv2d(8, 12)
+    assert tuple(m.weight.shape) == (9, 8, 12) and tuple(m.bias.shape) == (12,)
+    assert m.chunk_size == 4096
+    assert list(m.state_dict()) == ["weight", "bias"]
+    assert SparseConv2d(8, 12, bias=False).bias is None
+    assert tuple(SparseConv2d(8, 4, kernel_size=5).weight.shape) == (25, 8, 4)
+    sig = inspect.signature(SparseConv2dFunction.forward)
+    assert list(sig.parameters) == ["ctx", "x", "neighbor_indices", "weight", "bias", "tokens_per_batch", "chunk_size"]
+    with pytest.raises(ValueError):   # no CPU path, loudly
+        m(torch.zeros(4, 8), torch.zeros(4, 9, dtype=torch.int32))
+    from eccv26_tad_b200 import opentad_sparse_ops as shim
+    for name in ("fwd", "bwd_in", "bwd_w", "implicit_gemm_fwd_v2", "implicit_gemm_fwd_v2_chunked"):
+        assert callable(getattr(shim, name))
