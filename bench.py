@@ -1,0 +1,576 @@
+#!/usr/bin/env python
+"""SparseConv2D benchmark: retained tokens/s through forward + backward at keep 10/30/55 %.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the configuration the headline metric is quoted on): bf16 activations and weights with
+fp32 accumulate, batch 2, T=80 slices of a 14x14 token grid, C_in = C_out = 192, 3x3 taps, kept
+tokens chosen per slice as the top-k of N(0,1) scores at keep {10, 30, 55} % (3200 / 9440 / 17280
+retained tokens), features and upstream gradients N(0,1), Kaiming-normal weights.  One "step" runs
+forward, input gradient, weight + bias gradient for all three keep rates on one batch
+(29 920 retained tokens per GPU).  Data are synthetic and seeded; there is no dataset behind
+this op.  With N > 1 every rank owns its own batch (weak scaling, sharded by clip) and the
+weight / bias gradients are all-reduced over NCCL every step, as data-parallel training does.
+
+Numbers on the JSON line
+  value        tokens/s over all ranks with inputs already resident in HBM; every step reads a
+               different one of R input sets whose total size exceeds the L2, steps replayed as
+               CUDA graphs, timed with CUDA events, max over ranks
+  e2e          same metric through the public Python surface (build_neighbor_table + SparseConv2d
+               forward / backward under autograd) with HOST buffers: every step copies scores,
+               features and upstream gradients from pinned host memory and copies the outputs and
+               all gradients back
+  roofline     the dominant kernel (largest share of device time among forward / dgrad / wgrad),
+               dense-equivalent FLOPs 2*N*KK*Cin*Cout per launch over its CUDA-event duration,
+               against the measured bf16 peak in MEASURED_PEAKS.json (fallback 1590 TFLOP/s)
+  cpu_baseline the CPU oracle port (C, OpenMP, fp32 accumulate) timed on the host cores on a
+               bounded sample of the same workload (rank 0, N = 1 only)
+
+``--impl reference`` times that CPU port alone (the reference has no CPU implementation of this
+op; its CUDA path is reported under ``reference_cuda`` on the main line when the prebuilt
+extension under oracle/_ref/ is present).
+"""
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+KEEPS = (0.10, 0.30, 0.55)
+B, T, H, W, C, KS = 2, 80, 14, 14, 192, 3
+KK = KS * KS
+N_SETS = 8
+FALLBACK_TFLOPS = 1590.0
+FALLBACK_HBM = 6650.0
+METRIC = "SparseConv2D retained tokens/sec fwd+bwd at keep 10-55%"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture
+# summarised under profiles/ (None until a capture exists for the kernel that dominates)
+NCU_TRAFFIC_BYTES = {}
+
+
+def flops_pass(n):
+    return 2.0 * n * KK * C * C
+
+
+def num_keep(rate, L):
+    return max(0, min(int(math.ceil(rate * L)), L))
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d.get("bf16_tflops", FALLBACK_TFLOPS)), float(d.get("hbm_gbs", FALLBACK_HBM)), "measured"
+    return FALLBACK_TFLOPS, FALLBACK_HBM, "fallback"
+
+
+# ------------------------------------------------------------------------------------------ clocks
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed regions run."""
+
+    def __init__(self, device):
+        super().__init__(daemon=True)
+        self.samples = []
+        self.active = False
+        self.stop_flag = False
+        self.ok = False
+        self.max_mhz = None
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            try:
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(device).uuid)
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(device.index or 0)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            pass
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        while not self.stop_flag:
+            if self.active:
+                try:
+                    mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                    try:
+                        reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                    except Exception:
+                        reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                    self.samples.append((mhz, reasons))
+                except Exception:
+                    pass
+                time.sleep(0.002)
+            else:
+                time.sleep(0.005)
+
+    def summary(self):
+        if not self.ok or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        nv = self.nv
+        mhz = sorted(s[0] for s in self.samples)
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        seen = [k for k, bit in names.items() if any(s[1] & bit for s in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": self.max_mhz, "reasons": seen,
+                "samples": len(mhz)}
+
+
+# ------------------------------------------------------------------------------------------ data
+def make_host_sets(rank, n_sets, slices=B * T):
+    """Seeded CPU tensors: per set and keep rate the scores, features and upstream gradients."""
+    import torch
+    g = torch.Generator().manual_seed(1234 + 2 + 1000 * rank)
+    sets = []
+    for s in range(n_sets):
+        per_keep = []
+        for r in KEEPS:
+            k = num_keep(r, H * W)
+            n = slices * k
+            per_keep.append({
+                "k": k, "n": n,
+                "scores": torch.randn(slices, H * W, generator=g, dtype=torch.float32),
+                "x": torch.randn(n, C, generator=g, dtype=torch.float32).bfloat16(),
+                "gy": torch.randn(n, C, generator=g, dtype=torch.float32).bfloat16(),
+            })
+        sets.append(per_keep)
+    std = math.sqrt(2.0 / (C * KK))
+    w_conv = torch.randn(C, C, KS, KS, generator=torch.Generator().manual_seed(77), dtype=torch.float32) * std
+    weight = w_conv.view(C, C, KK).permute(2, 1, 0).contiguous()
+    return sets, weight, torch.zeros(C)
+
+
+# ------------------------------------------------------------------------------------------ CPU arm
+def cpu_port_run(steps, warmup, slices):
+    """Times the C/OpenMP oracle port (fp32 accumulate) on `slices` slices per keep rate."""
+    import torch
+    from oracle import conv as oconv
+    from oracle import table as otab
+    sets, weight, bias = make_host_sets(0, 1, slices)
+    wf = weight.bfloat16().float().numpy()
+    bf = bias.numpy()
+    work = []
+    tokens = 0
+    for item in sets[0]:
+        kept, table = otab.build_table(item["scores"].numpy(), item["k"], H, W, KS)
+        work.append((item["x"].float().numpy(), item["gy"].float().numpy(), table))
+        tokens += item["n"]
+
+    def step():
+        for x, gy, table in work:
+            oconv.fwd(x, table, wf, bf, acc="f32")
+            oconv.dgrad(gy, table, wf, acc="f32")
+            oconv.wgrad(gy, x, table, KK, acc="f32")
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = time.perf_counter() - t0
+    cores = len(os.sched_getaffinity(0))
+    return tokens * steps / dt, dt / steps * 1e3, cores, tokens
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    slices = 40   # a quarter of the workload's 160 slices per step
+    value, ms, cores, tokens = cpu_port_run(args.steps, args.warmup, slices)
+    sample = (f"{slices} of {B * T} slices per keep rate ({tokens} retained tokens per step), "
+              f"C oracle port of the kernel math, OpenMP over {cores} threads; the reference has no CPU path")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.gpus, note="CPU port, bounded sample"),
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def workload_config(n_gpus, note=None):
+    cfg = {
+        "workload": "SparseConv2D fwd+bwd bf16 (fp32 accumulate): batch 2 x T=80 slices x 14x14 grid per GPU, "
+                    "Cin=Cout=192, 3x3, keep sweep {10,30,55}% by per-slice top-k",
+        "tokens_per_step_per_gpu": sum(B * T * num_keep(r, H * W) for r in KEEPS),
+        "keep_rates": list(KEEPS),
+        "parallelism": f"dp{n_gpus} (sharded by clip; NCCL all-reduce of weight/bias gradients)" if n_gpus > 1 else "single GPU",
+        "l2": f"inputs larger than L2: every step reads a different one of {N_SETS} resident input sets (~{N_SETS * 47} MB > 126 MB)",
+    }
+    if note:
+        cfg["note"] = note
+    return cfg
+
+
+# ------------------------------------------------------------------------------------------ GPU arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying CUDA graphs")
+    ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--skip-ref-cuda", action="store_true")
+    ap.add_argument("--kernel-case", default=None, choices=["fwd", "dgrad", "wgrad", "table"],
+                    help="profiling aid: launch only this kernel a few times on --case-slices slices and exit")
+    ap.add_argument("--case-slices", type=int, default=3840)
+    ap.add_argument("--case-keep", type=float, default=0.30)
+    ap.add_argument("--case-launches", type=int, default=4)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.kernel_case:
+        return kernel_case(args)
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    from eccv26_tad_b200 import SparseConv2d, build_neighbor_table, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    sampler = ClockSampler(dev)
+    sampler.start()
+
+    host_sets, weight_h, bias_h = make_host_sets(rank, N_SETS)
+    weight = weight_h.bfloat16().to(dev)
+    bias = bias_h.bfloat16().to(dev)
+    tokens_step = sum(it["n"] for it in host_sets[0])
+
+    # resident device sets: table built once per set by the CUDA builder, inputs and outputs preallocated
+    dsets = []
+    for per_keep in host_sets:
+        dk = []
+        for it in per_keep:
+            scores = it["scores"].to(dev)
+            kept, table = build_neighbor_table(scores, num_keep=it["k"], h=H, w=W, kernel_size=KS)
+            dk.append({"n": it["n"], "table": table, "x": it["x"].to(dev), "gy": it["gy"].to(dev)})
+        dsets.append(dk)
+    lib = ops._lib.load()
+    code = ops._lib.BF16
+    ws_bytes = max(lib.svtad_workspace_bytes(ops._lib.OP_WGRAD, it["n"], C, C, KK, code) for it in host_sets[0])
+    ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+    n_max = max(it["n"] for it in host_sets[0])
+    y_buf = torch.empty(n_max, C, dtype=torch.bfloat16, device=dev)
+    gx_buf = torch.empty(n_max, C, dtype=torch.bfloat16, device=dev)
+    grads = torch.empty(KK * C * C + C, dtype=torch.bfloat16, device=dev)   # gw ++ gb, one all-reduce bucket
+    gw_buf, gb_buf = grads[:KK * C * C], grads[KK * C * C:]
+    launches_per_step = 0
+
+    def raw_step(dk, stream, count=False):
+        """One step through the C ABI on resident buffers: 3 keep rates x (fwd, dgrad, wgrad+bias)."""
+        nl = 0
+        for it in dk:
+            n = it["n"]
+            ops._lib.check(lib.svtad_conv_fwd(it["x"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(),
+                                              bias.data_ptr(), y_buf.data_ptr(), n, C, C, KK, 0, code, None, 0, stream))
+            ops._lib.check(lib.svtad_conv_dgrad(it["gy"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(),
+                                                gx_buf.data_ptr(), n, C, C, KK, 0, code, None, None, 0, stream))
+            ops._lib.check(lib.svtad_conv_wgrad(it["gy"].data_ptr(), it["x"].data_ptr(), it["table"].data_ptr(),
+                                                gw_buf.data_ptr(), gb_buf.data_ptr(), n, C, C, KK, 0, code,
+                                                ws.data_ptr(), ws_bytes, stream))
+            nl += 5   # fwd, dgrad, wgrad partial, bias partial, finalize
+            if world > 1:
+                dist.all_reduce(grads)
+        return nl
+
+    stream = torch.cuda.Stream(device=dev)
+    graphs = None
+    with torch.cuda.stream(stream):
+        for s in range(min(3, N_SETS)):
+            launches_per_step = raw_step(dsets[s], stream.cuda_stream)
+        stream.synchronize()
+        if not args.no_graph:
+            try:
+                graphs = []
+                for s in range(N_SETS):
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=stream):
+                        raw_step(dsets[s], torch.cuda.current_stream().cuda_stream)
+                    graphs.append(g)
+            except Exception as e:   # stay measurable without graphs
+                sys.stderr.write(f"[bench] CUDA graph capture failed ({e}); launching eagerly\n")
+                graphs = None
+                torch.cuda.synchronize()
+
+    def run_steps(k, first):
+        for i in range(k):
+            s = (first + i) % N_SETS
+            if graphs is not None:
+                graphs[s].replay()
+            else:
+                raw_step(dsets[s], torch.cuda.current_stream().cuda_stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---------------------------------------------------------------- timed region (device resident)
+    with torch.cuda.stream(stream):
+        run_steps(args.warmup, 0)
+        barrier()
+        sampler.active = True
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        run_steps(args.steps, args.warmup)
+        e1.record(stream)
+        barrier()
+        ms_total = e0.elapsed_time(e1)
+        # keep the GPU under the same load a little longer so the clock sampler sees it
+        t_end = time.perf_counter() + 0.25
+        while time.perf_counter() < t_end:
+            run_steps(20, 0)
+            torch.cuda.synchronize()
+        sampler.active = False
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    value = world * tokens_step * args.steps / (ms_total * 1e-3)
+
+    # ---------------------------------------------------------------- per-kernel durations (instrumented repeat)
+    def time_op(fn, reps):
+        with torch.cuda.stream(stream):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            tot = 0.0
+            for i in range(reps):
+                a.record(stream)
+                fn(i)
+                b.record(stream)
+                b.synchronize()
+                tot += a.elapsed_time(b)
+            return tot / reps
+
+    sc = stream.cuda_stream
+    per_kernel = {}
+    reps = 24
+    for ki, r in enumerate(KEEPS):
+        def f_fwd(i, ki=ki):
+            it = dsets[i % N_SETS][ki]
+            lib.svtad_conv_fwd(it["x"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                               y_buf.data_ptr(), it["n"], C, C, KK, 0, code, None, 0, sc)
+
+        def f_dg(i, ki=ki):
+            it = dsets[i % N_SETS][ki]
+            lib.svtad_conv_dgrad(it["gy"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(), gx_buf.data_ptr(),
+                                 it["n"], C, C, KK, 0, code, None, None, 0, sc)
+
+        def f_wg(i, ki=ki):
+            it = dsets[i % N_SETS][ki]
+            lib.svtad_conv_wgrad(it["gy"].data_ptr(), it["x"].data_ptr(), it["table"].data_ptr(), gw_buf.data_ptr(),
+                                 gb_buf.data_ptr(), it["n"], C, C, KK, 0, code, ws.data_ptr(), ws_bytes, sc)
+
+        for name, fn in (("fwd", f_fwd), ("dgrad", f_dg), ("wgrad", f_wg)):
+            time_op(fn, 3)
+            per_kernel[(name, ki)] = time_op(fn, reps)
+    torch.cuda.synchronize()
+    totals = {name: sum(per_kernel[(name, ki)] for ki in range(len(KEEPS))) for name in ("fwd", "dgrad", "wgrad")}
+    dominant = max(totals, key=totals.get)
+    peak_tf, peak_hbm, peak_kind = measured_peaks()
+    dom_flops = sum(flops_pass(host_sets[0][ki]["n"]) for ki in range(len(KEEPS)))
+    achieved = dom_flops / (totals[dominant] * 1e-3) / 1e12
+    roofline = {
+        "bound": "tensor", "kernel": {"fwd": "conv_tc_kernel<BN,false>", "dgrad": "conv_tc_kernel<BN,true>",
+                                      "wgrad": "wgrad_tc_kernel<BN> (+ bias partial + finalize)"}[dominant],
+        "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
+        "peak_source": f"{peak_kind} bf16 burst", "traffic": NCU_TRAFFIC_BYTES.get(dominant),
+        "flops_per_launch": {f"keep{int(r * 100)}": flops_pass(host_sets[0][ki]["n"]) for ki, r in enumerate(KEEPS)},
+        "ms_per_launch": {f"{name}_keep{int(KEEPS[ki] * 100)}": v for (name, ki), v in per_kernel.items()},
+        "all_kernels_frac": {name: dom_flops / (totals[name] * 1e-3) / 1e12 / peak_tf for name in totals},
+    }
+
+    # ---------------------------------------------------------------- e2e through the public API, host buffers
+    module = SparseConv2d(C, C).to(dev)
+    with torch.no_grad():
+        module.weight.copy_(weight_h)
+        module.bias.copy_(bias_h)
+    pin = []
+    for per_keep in host_sets:
+        pk = []
+        for it in per_keep:
+            pk.append({k: (v.pin_memory() if hasattr(v, "pin_memory") else v) for k, v in it.items()})
+        pin.append(pk)
+    out_h = [{"y": torch.empty(it["n"], C, dtype=torch.bfloat16).pin_memory(),
+              "gx": torch.empty(it["n"], C, dtype=torch.bfloat16).pin_memory()} for it in host_sets[0]]
+    gw_h = torch.empty(KK, C, C, dtype=torch.float32).pin_memory()
+    gb_h = torch.empty(C, dtype=torch.float32).pin_memory()
+    h2d = sum(it["scores"].numel() * 4 + it["x"].numel() * 2 + it["gy"].numel() * 2 for it in host_sets[0])
+    d2h = sum(2 * it["n"] * C * 2 for it in host_sets[0]) + 3 * (gw_h.numel() * 4 + gb_h.numel() * 4)
+
+    def e2e_step(si):
+        for ki, it in enumerate(pin[si % N_SETS]):
+            scores = it["scores"].to(dev, non_blocking=True)
+            x = it["x"].to(dev, non_blocking=True).requires_grad_(True)
+            gy = it["gy"].to(dev, non_blocking=True)
+            kept, table = build_neighbor_table(scores, num_keep=it["k"], h=H, w=W, kernel_size=KS)
+            module.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                y = module(x, table)
+            y.backward(gy)
+            if world > 1:
+                dist.all_reduce(module.weight.grad)
+                dist.all_reduce(module.bias.grad)
+            out_h[ki]["y"].copy_(y, non_blocking=True)
+            out_h[ki]["gx"].copy_(x.grad, non_blocking=True)
+            gw_h.copy_(module.weight.grad, non_blocking=True)
+            gb_h.copy_(module.bias.grad, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    e2e_steps = max(3, min(args.steps, 50))
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    sampler.active = True
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(e2e_steps):
+        e2e_step(3 + i)
+    b.record()
+    barrier()
+    sampler.active = False
+    e2e_ms = a.elapsed_time(b)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = world * tokens_step * e2e_steps / (e2e_ms * 1e-3)
+    sampler.stop_flag = True
+    assert ops.device_error() == 0, "a bounded wait inside a tensor-core kernel gave up"
+
+    # ---------------------------------------------------------------- reference CUDA path on the same GPU (rank 0)
+    ref_cuda = None
+    if rank == 0 and not args.skip_ref_cuda:
+        try:
+            ref_cuda = time_reference_cuda(dsets, weight, bias, stream)
+        except Exception as e:
+            ref_cuda = {"unavailable": str(e)[:200]}
+
+    # ---------------------------------------------------------------- CPU baseline (rank 0, N = 1)
+    cpu = None
+    if rank == 0 and world == 1 and not args.skip_cpu:
+        slices = 40
+        v, ms, cores, tokens = cpu_port_run(3, 1, slices)
+        cpu = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
+               "sample": f"{slices} of {B * T} slices per keep rate ({tokens} tokens per step, 3 steps), C oracle port, OpenMP"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": dict(workload_config(world), launch="cuda_graph" if graphs is not None else "eager"),
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": roofline, "cpu_baseline": cpu, "reference_cuda": ref_cuda,
+            "clocks": sampler.summary(),
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def kernel_case(args):
+    """A few launches of one kernel on one large seeded case (for ncu captures; prints timings only)."""
+    import torch
+    from eccv26_tad_b200 import build_neighbor_table, ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator().manual_seed(99)
+    slices = args.case_slices
+    k = num_keep(args.case_keep, H * W)
+    scores = torch.randn(slices, H * W, generator=g).to(dev)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.case_launches + 1)]
+    if args.kernel_case == "table":
+        ev[0].record()
+        for i in range(args.case_launches):
+            kept, table = build_neighbor_table(scores, num_keep=k, h=H, w=W, kernel_size=KS)
+            ev[i + 1].record()
+        torch.cuda.synchronize()
+        n = slices * k
+        bytes_ = 4 * slices * H * W + 4 * n + 4 * n * KK
+        ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.case_launches)]
+        print(json.dumps({"kernel_case": "table", "slices": slices, "rows": n, "ms": ms,
+                          "algorithmic_bytes": bytes_, "GB/s_best": bytes_ / (min(ms) * 1e-3) / 1e9}))
+        return
+    kept, table = build_neighbor_table(scores, num_keep=k, h=H, w=W, kernel_size=KS)
+    n = table.shape[0]
+    x = torch.randn(n, C, device=dev).bfloat16()
+    gy = torch.randn(n, C, device=dev).bfloat16()
+    w = (torch.randn(KK, C, C, device=dev) * math.sqrt(2.0 / (C * KK))).bfloat16()
+    b = torch.zeros(C, device=dev).bfloat16()
+    ev[0].record()
+    for i in range(args.case_launches):
+        if args.kernel_case == "fwd":
+            ops.conv_fwd(x, table, w, b)
+        elif args.kernel_case == "dgrad":
+            ops.conv_dgrad(gy, table, w, assume_symmetric=True)
+        else:
+            ops.conv_wgrad(gy, x, table, KK)
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.case_launches)]
+    print(json.dumps({"kernel_case": args.kernel_case, "slices": slices, "rows": n, "ms": ms,
+                      "flops": flops_pass(n), "TFLOP/s_best": flops_pass(n) / (min(ms) * 1e-3) / 1e12}))
+
+
+def time_reference_cuda(dsets, weight, bias, stream):
+    """The reference's own CUDA extension (prebuilt under oracle/_ref/) on the same resident inputs."""
+    import torch
+    from oracle import build_ref
+    mod = build_ref.load_built()
+    if mod is None:
+        return {"unavailable": "oracle/_ref extension not built"}
+    reps = 5
+    tokens = sum(it["n"] for it in dsets[0])
+
+    def step(dk):
+        for it in dk:
+            n = it["n"]
+            mod.implicit_gemm_fwd_v2_chunked(it["x"], it["table"], weight, bias, 0, 4096)
+            mod.bwd_in(it["gy"], it["table"], weight, n, C, 0)
+            mod.bwd_w(it["gy"], it["x"], it["table"], C, 0)
+            it["gy"].sum(0)
+    # the reference launches on the legacy default stream: time on it
+    torch.cuda.synchronize()
+    step(dsets[0])
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(reps):
+        step(dsets[(i + 1) % N_SETS])
+    b.record()
+    torch.cuda.synchronize()
+    ms = a.elapsed_time(b) / reps
+    return {"value": tokens / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms, "steps": reps,
+            "what": "reference extension (implicit_gemm_fwd_v2_chunked + bwd_in + bwd_w + sum) recompiled for sm_100a, eager launches"}
+
+
+if __name__ == "__main__":
+    main()

@@ -62,11 +62,12 @@ conv_simt_kernel(const T* __restrict__ a, const int32_t* __restrict__ nbr, const
     }
     __syncthreads();
 
-    float acc[4][4];
+    // acc holds one tap's partial sum; tot collects the taps (shorter fp32 chains, smaller error)
+    float acc[4][4], tot[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+        for (int j = 0; j < 4; ++j) { acc[i][j] = 0.f; tot[i][j] = 0.f; }
 
     for (int k = 0; k < kk; ++k) {
         if (!s_any[k]) continue;
@@ -160,6 +161,11 @@ conv_simt_kernel(const T* __restrict__ a, const int32_t* __restrict__ nbr, const
 #pragma unroll
                 for (int q = 0; q < 4; ++q) acc[i][q] = 0.f;
             }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { tot[i][q] += acc[i][q]; acc[i][q] = 0.f; }
         }
     }
     if (MODE == MODE_DSCATTER) return;
@@ -177,19 +183,18 @@ conv_simt_kernel(const T* __restrict__ a, const int32_t* __restrict__ nbr, const
         if (row >= n) continue;
         T* dst = out + row * cn + col;
         if (col + 3 < cn && (cn & 3) == 0) {
-            Cvt<T>::store4(dst, make_float4(acc[i][0] + b4[0], acc[i][1] + b4[1],
-                                            acc[i][2] + b4[2], acc[i][3] + b4[3]));
+            Cvt<T>::store4(dst, make_float4(tot[i][0] + b4[0], tot[i][1] + b4[1],
+                                            tot[i][2] + b4[2], tot[i][3] + b4[3]));
         } else {
 #pragma unroll
             for (int q = 0; q < 4; ++q)
-                if (col + q < cn) Cvt<T>::store1(dst + q, acc[i][q] + b4[q]);
+                if (col + q < cn) Cvt<T>::store1(dst + q, tot[i][q] + b4[q]);
         }
     }
 }
 
-// In the DSCATTER mode s_any must be "all taps with any valid entry"; the loader above marks a tap
-// only from the A-row index (always valid), so every tap is visited and invalid entries are
-// skipped at scatter time.
+// In the DSCATTER mode the A rows are the tile's own rows, so every tap is visited and entries that
+// are -1 or out of range are skipped when the tap's result is scattered.
 
 template <typename T>
 __global__ void cast_ws_kernel(const float* __restrict__ ws, T* __restrict__ out, long total,

@@ -57,7 +57,7 @@ def test_against_reference_cuda(ref, dtype, C, B, T, keep):
     xf, wf, bf, gf = (f32np(t) for t in (x, w, b, gy))
     truth = (oconv.fwd(xf, tn, wf, bf), oconv.dgrad(gf, tn, wf), oconv.wgrad(gf, xf, tn, 9, with_bias=False)[0])
     tol = 1e-5 if dtype == torch.float32 else 2e-2
-    unit = 1e-6 if dtype == torch.float32 else 4e-3
+    unit = 2e-6 if dtype == torch.float32 else 4e-3
     for name, m, r, t in zip(("y", "gx", "gw"), mine, theirs, truth):
         em, er = oconv.rel_err(f32np(m), t), oconv.rel_err(f32np(r), t)
         assert em < tol, f"{name}: new kernel err {em:.3e}"
