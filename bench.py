@@ -356,16 +356,16 @@ def main():
 
     # ---------------------------------------------------------------- per-kernel durations (instrumented repeat)
     def time_op(fn, reps):
+        # `reps` launches back to back between two events, each on a different resident input set
         with torch.cuda.stream(stream):
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            tot = 0.0
+            stream.synchronize()
+            a.record(stream)
             for i in range(reps):
-                a.record(stream)
                 fn(i)
-                b.record(stream)
-                b.synchronize()
-                tot += a.elapsed_time(b)
-            return tot / reps
+            b.record(stream)
+            b.synchronize()
+            return a.elapsed_time(b) / reps
 
     sc = stream.cuda_stream
     per_kernel = {}

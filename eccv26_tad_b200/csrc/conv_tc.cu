@@ -28,7 +28,7 @@ constexpr int TC_THREADS = 288;        // 4 A-producer warps, 4 B-producer warps
 constexpr int TILE_M = 128;
 constexpr int STAGE_K = 64;            // 64 x 16-bit = one 128-byte swizzle row
 constexpr int A_TILE_BYTES = TILE_M * 128;
-constexpr int LAG = 2;                 // cp.async groups kept in flight per producer thread
+constexpr int LAG = 2;                 // writer-fence protocol only: cp.async groups in flight per thread
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // about two seconds
 
 // ---------------------------------------------------------------------------------------------
@@ -73,6 +73,11 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
 }
+// Arrival on `bar` that fires when all cp.async copies issued so far by this thread have landed; the
+// barrier's expected count already includes it (.noinc), so the issuing thread never blocks.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -107,6 +112,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
           "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -145,6 +158,8 @@ __device__ __forceinline__ float widen(uint16_t v, bool fp16) {
     return __uint_as_float(static_cast<uint32_t>(v) << 16);
 }
 
+// bytes of one B stage: MN-major tiles are whole 64-column blocks of 8 KB, K-major tiles BN rows of 128 B
+constexpr int b_tile_bytes_for(int bn) { return ((bn + 63) / 64) * 8192; }
 constexpr int tmem_cols_for(int bn) { return bn <= 32 ? 32 : bn <= 64 ? 64 : bn <= 128 ? 128 : 256; }
 
 struct TcSmemTail {            // lives after the stage ring in dynamic shared memory
@@ -164,12 +179,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const uint16_t* __restrict__ a, const int32_t* __restrict__ nbr,
                const uint16_t* __restrict__ w, const uint16_t* __restrict__ bias,
                uint16_t* __restrict__ out, const int32_t* __restrict__ status, long n, int cred,
-               int cn, int cin, int cout, int kk, int tpb, int nstage, int fp16) {
+               int cn, int cin, int cout, int kk, int tpb, int nstage, int fp16, int writer_fence) {
     if (DGRAD && status != nullptr && (__ldg(status) & SVTAD_TABLE_ASYMMETRIC)) return;
-    constexpr int B_TILE_BYTES = BN * 128;
+    constexpr int B_TILE_BYTES = b_tile_bytes_for(BN);
     constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
     constexpr int TM_COLS = tmem_cols_for(BN);
-    constexpr int HALF = BN / 2;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -270,19 +284,25 @@ conv_tc_kernel(const uint16_t* __restrict__ a, const int32_t* __restrict__ nbr,
                         cp_async16(dst, src, 16u);
                     }
                 }
-                cp_async_commit();
-                if (it >= LAG) {
-                    cp_async_wait<LAG>();
-                    fence_proxy_async();
-                    mbar_arrive(smem_u32(&tail->full[(it - LAG) % nstage]));
+                if (!writer_fence) {
+                    cp_async_arrive_noinc(smem_u32(&tail->full[s]));
+                } else {
+                    cp_async_commit();
+                    if (it >= LAG) {
+                        cp_async_wait<LAG>();
+                        fence_proxy_async();
+                        mbar_arrive(smem_u32(&tail->full[(it - LAG) % nstage]));
+                    }
                 }
             }
         }
-        cp_async_wait<0>();
-        fence_proxy_async();
-        if (alive) {
-            int first = total_stages - LAG < 0 ? 0 : total_stages - LAG;
-            for (int j = first; j < total_stages; ++j) mbar_arrive(smem_u32(&tail->full[j % nstage]));
+        if (writer_fence) {
+            cp_async_wait<0>();
+            fence_proxy_async();
+            if (alive) {
+                int first = total_stages - LAG < 0 ? 0 : total_stages - LAG;
+                for (int j = first; j < total_stages; ++j) mbar_arrive(smem_u32(&tail->full[j % nstage]));
+            }
         }
 
         // ------------------------------------------------------------------ epilogue
@@ -292,20 +312,21 @@ conv_tc_kernel(const uint16_t* __restrict__ a, const int32_t* __restrict__ nbr,
         if (have) {
             const int q = warp & 3, hsel = warp >> 2;
             const long row = row0 + q * 32 + lane;
+            // warps w and w+4 share a lane quarter and alternate over the 16-column chunks
 #pragma unroll 1
-            for (int cbase = hsel * HALF; cbase < (hsel + 1) * HALF; cbase += 32) {
-                uint32_t v[32];
+            for (int cbase = hsel * 16; cbase < BN; cbase += 32) {
+                uint32_t v[16];
                 if (total_stages > 0) {
-                    tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + cbase, v);
+                    tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + cbase, v);
                     tmem_ld_wait();
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) v[j] = 0u;
+                    for (int j = 0; j < 16; ++j) v[j] = 0u;
                 }
                 if (row < n) {
                     uint4* dst = reinterpret_cast<uint4*>(out + row * cn + n0 + cbase);
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
+                    for (int g = 0; g < 2; ++g) {
                         uint4 o;
                         o.x = pack2(__uint_as_float(v[g * 8 + 0]) + s_bias[cbase + g * 8 + 0],
                                     __uint_as_float(v[g * 8 + 1]) + s_bias[cbase + g * 8 + 1], fp16 != 0);
@@ -327,6 +348,7 @@ conv_tc_kernel(const uint16_t* __restrict__ a, const int32_t* __restrict__ nbr,
         for (int it = 0; it < total_stages; ++it) {
             const int s = it % nstage;
             if (!mbar_wait(smem_u32(&tail->full[s]), (it / nstage) & 1, s_abort, 2)) { alive = false; break; }
+            fence_proxy_async();   // cp.async (generic proxy) writes -> tcgen05.mma (async proxy) reads
             tc_fence_after();
             const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
             const uint32_t b_tile = a_tile + A_TILE_BYTES;
@@ -341,6 +363,7 @@ conv_tc_kernel(const uint16_t* __restrict__ a, const int32_t* __restrict__ nbr,
         }
         if (alive && total_stages > 0) umma_commit(smem_u32(&tail->accum));
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
     tc_fence_before();
     __syncthreads();
     if (warp == 8) {
@@ -357,11 +380,11 @@ template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 wgrad_tc_kernel(const uint16_t* __restrict__ gy, const uint16_t* __restrict__ x,
                 const int32_t* __restrict__ nbr, float* __restrict__ ws, long n, int cin, int cout,
-                int kk, int tpb, long tokens_per_split, int n_nblk, int nstage, int fp16) {
-    constexpr int B_TILE_BYTES = BN * 128;
+                int kk, int tpb, long tokens_per_split, int n_nblk, int nstage, int fp16,
+                int writer_fence) {
+    constexpr int B_TILE_BYTES = b_tile_bytes_for(BN);
     constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
     constexpr int TM_COLS = tmem_cols_for(BN);
-    constexpr int HALF = BN / 2;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -443,11 +466,15 @@ wgrad_tc_kernel(const uint16_t* __restrict__ gy, const uint16_t* __restrict__ x,
                     const uint16_t* src = x + (long)(j < 0 ? 0 : j) * cin + ch0[h] + sub * 8;
                     cp_async16(dst0 + itr * 2048, src, j < 0 ? 0u : 16u);
                 }
-                cp_async_commit();
-                if (it >= LAG) {
-                    cp_async_wait<LAG>();
-                    fence_proxy_async();
-                    mbar_arrive(smem_u32(&tail->full[(it - LAG) % nstage]));
+                if (!writer_fence) {
+                    cp_async_arrive_noinc(smem_u32(&tail->full[s]));
+                } else {
+                    cp_async_commit();
+                    if (it >= LAG) {
+                        cp_async_wait<LAG>();
+                        fence_proxy_async();
+                        mbar_arrive(smem_u32(&tail->full[(it - LAG) % nstage]));
+                    }
                 }
 #pragma unroll
                 for (int itr = 0; itr < 8; ++itr) cur[itr] = nxt[itr];
@@ -469,19 +496,25 @@ wgrad_tc_kernel(const uint16_t* __restrict__ gy, const uint16_t* __restrict__ x,
                     uint32_t dst = b_tile + (cc >> 3) * 8192 + r * 128 + (((cc & 7) ^ (r & 7)) << 4);
                     cp_async16(dst, src, ok ? 16u : 0u);
                 }
-                cp_async_commit();
-                if (it >= LAG) {
-                    cp_async_wait<LAG>();
-                    fence_proxy_async();
-                    mbar_arrive(smem_u32(&tail->full[(it - LAG) % nstage]));
+                if (!writer_fence) {
+                    cp_async_arrive_noinc(smem_u32(&tail->full[s]));
+                } else {
+                    cp_async_commit();
+                    if (it >= LAG) {
+                        cp_async_wait<LAG>();
+                        fence_proxy_async();
+                        mbar_arrive(smem_u32(&tail->full[(it - LAG) % nstage]));
+                    }
                 }
             }
         }
-        cp_async_wait<0>();
-        fence_proxy_async();
-        if (alive) {
-            int first = total_stages - LAG < 0 ? 0 : total_stages - LAG;
-            for (int j = first; j < total_stages; ++j) mbar_arrive(smem_u32(&tail->full[j % nstage]));
+        if (writer_fence) {
+            cp_async_wait<0>();
+            fence_proxy_async();
+            if (alive) {
+                int first = total_stages - LAG < 0 ? 0 : total_stages - LAG;
+                for (int j = first; j < total_stages; ++j) mbar_arrive(smem_u32(&tail->full[j % nstage]));
+            }
         }
 
         // epilogue: fp32 partial tile -> workspace[split][(tap, ci)][co]
@@ -495,18 +528,18 @@ wgrad_tc_kernel(const uint16_t* __restrict__ gy, const uint16_t* __restrict__ x,
                 const long grow = (long)(blk / cblocks) * cin + (blk % cblocks) * 64 + (q & 1) * 32 + lane;
                 float* dstrow = ws + ((long)blockIdx.y * kk * cin + grow) * cout + n0;
 #pragma unroll 1
-                for (int cbase = hsel * HALF; cbase < (hsel + 1) * HALF; cbase += 32) {
-                    uint32_t v[32];
+                for (int cbase = hsel * 16; cbase < BN; cbase += 32) {
+                    uint32_t v[16];
                     if (total_stages > 0) {
-                        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + cbase, v);
+                        tmem_ld16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + cbase, v);
                         tmem_ld_wait();
                     } else {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) v[j] = 0u;
+                        for (int j = 0; j < 16; ++j) v[j] = 0u;
                     }
                     uint4* dst = reinterpret_cast<uint4*>(dstrow + cbase);
 #pragma unroll
-                    for (int g = 0; g < 8; ++g) dst[g] = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                    for (int g = 0; g < 4; ++g) dst[g] = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
                 }
             }
         }
@@ -516,6 +549,7 @@ wgrad_tc_kernel(const uint16_t* __restrict__ gy, const uint16_t* __restrict__ x,
         for (int it = 0; it < total_stages; ++it) {
             const int s = it % nstage;
             if (!mbar_wait(smem_u32(&tail->full[s]), (it / nstage) & 1, s_abort, 14)) { alive = false; break; }
+            fence_proxy_async();
             tc_fence_after();
             const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
             const uint32_t b_tile = a_tile + A_TILE_BYTES;
@@ -529,6 +563,7 @@ wgrad_tc_kernel(const uint16_t* __restrict__ gy, const uint16_t* __restrict__ x,
         }
         if (alive && total_stages > 0) umma_commit(smem_u32(&tail->accum));
     }
+    asm volatile("cp.async.wait_all;" ::: "memory");
     tc_fence_before();
     __syncthreads();
     if (warp == 8) {
@@ -543,22 +578,49 @@ wgrad_tc_kernel(const uint16_t* __restrict__ gy, const uint16_t* __restrict__ x,
 // ---------------------------------------------------------------------------------------------
 constexpr size_t SMEM_LIMIT = 227 * 1024;
 
+static int num_sms() {
+    static int cached = 0;
+    if (cached == 0) {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
+            cached = v;
+        else
+            cached = 148;
+    }
+    return cached;
+}
+
+static bool writer_fence_mode() {
+    const char* e = getenv("SVTAD_TC_WRITER_FENCE");
+    return e != nullptr && *e == '1';
+}
+
+// Column-block width of a forward / dgrad CTA.  One CTA runs per SM, so the cost of a choice is
+// (waves over the SMs) x (bytes a CTA stages per K step: 16 KB of gathered rows + its weight tile).
 static int pick_bn(int cn, long m_tiles) {
+    const int cand[5] = {256, 192, 128, 96, 64};
     const char* e = getenv("SVTAD_TC_BN");
     if (e != nullptr && *e) {
         int v = atoi(e);
-        if ((v == 64 || v == 128 || v == 192 || v == 256) && cn % v == 0) return v;
+        for (int c : cand)
+            if (v == c && cn % v == 0) return v;
     }
-    const int cand[4] = {256, 192, 128, 64};
-    for (int c : cand)
-        if (cn % c == 0 && m_tiles * (cn / c) >= 120) return c;
-    for (int i = 3; i >= 0; --i)
-        if (cn % cand[i] == 0) return cand[i];
-    return 0;
+    const long sms = num_sms();
+    int best = 0;
+    long best_cost = 0;
+    for (int c : cand) {
+        if (cn % c != 0) continue;
+        long ctas = m_tiles * (cn / c);
+        long waves = (ctas + sms - 1) / sms;
+        long cost = waves * (A_TILE_BYTES + b_tile_bytes_for(c));
+        if (best == 0 || cost < best_cost) { best = c; best_cost = cost; }
+    }
+    return best;
 }
 
 static int stages_for(int bn, size_t extra) {
-    size_t stage = A_TILE_BYTES + (size_t)bn * 128;
+    size_t stage = A_TILE_BYTES + (size_t)b_tile_bytes_for(bn);
     size_t avail = SMEM_LIMIT - 1024 - sizeof(TcSmemTail) - extra;
     int s = (int)(avail / stage);
     return s > 8 ? 8 : s;
@@ -580,14 +642,14 @@ static int launch_conv_tc(const ConvArgs& p, const int32_t* status, cudaStream_t
     int nstage = stages_for(BN, extra);
     if (nstage < LAG + 2)
         return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core conv: not enough shared memory for BN=%d kk=%d", BN, p.kk);
-    size_t smem = 1024 + (size_t)nstage * (A_TILE_BYTES + BN * 128) + sizeof(TcSmemTail) + extra;
+    size_t smem = 1024 + (size_t)nstage * (A_TILE_BYTES + b_tile_bytes_for(BN)) + sizeof(TcSmemTail) + extra;
     auto kern = conv_tc_kernel<BN, DGRAD>;
     SV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)((p.n + TILE_M - 1) / TILE_M), (unsigned)(cn / BN));
     kern<<<grid, TC_THREADS, smem, s>>>((const uint16_t*)p.a, p.nbr, (const uint16_t*)p.w,
                                         (const uint16_t*)p.bias, (uint16_t*)p.out, status, (long)p.n,
                                         cred, cn, p.cin, p.cout, p.kk, p.tpb, nstage,
-                                        p.dtype == SVTAD_F16 ? 1 : 0);
+                                        p.dtype == SVTAD_F16 ? 1 : 0, writer_fence_mode() ? 1 : 0);
     SV_LAUNCH_CHECK("conv_tc_kernel");
     return SVTAD_OK;
 }
@@ -598,6 +660,7 @@ static int dispatch_conv_tc(const ConvArgs& p, const int32_t* status, cudaStream
     int bn = pick_bn(cn, (p.n + TILE_M - 1) / TILE_M);
     switch (bn) {
         case 64: return launch_conv_tc<64, DGRAD>(p, status, s);
+        case 96: return launch_conv_tc<96, DGRAD>(p, status, s);
         case 128: return launch_conv_tc<128, DGRAD>(p, status, s);
         case 192: return launch_conv_tc<192, DGRAD>(p, status, s);
         case 256: return launch_conv_tc<256, DGRAD>(p, status, s);
@@ -620,13 +683,20 @@ static WgradPlan wgrad_plan(int64_t n, int cin, int cout, int kk) {
     int nblocks = kk * (cin / 64);
     pl.n_pairs = (nblocks + 1) / 2;
     long ctas = (long)pl.n_pairs * pl.n_nblk;
-    long want = (148 + ctas - 1) / ctas;
-    const char* e = getenv("SVTAD_TC_WGRAD_SPLITS");
-    if (e != nullptr && *e && atoi(e) > 0) want = atoi(e);
+    const long sms = num_sms();
     long max_by_rows = (n + 2 * STAGE_K - 1) / (2 * STAGE_K);
-    long s = want < max_by_rows ? want : max_by_rows;
-    if (s < 1) s = 1;
-    if (s > 64) s = 64;
+    if (max_by_rows < 1) max_by_rows = 1;
+    if (max_by_rows > 64) max_by_rows = 64;
+    // splits over tokens: minimise (waves over the SMs) x (tokens per split), ties to fewer splits
+    long s = 1;
+    double best = 0;
+    for (long c = 1; c <= max_by_rows; ++c) {
+        long waves = (ctas * c + sms - 1) / sms;
+        double cost = (double)waves * (double)((n + c - 1) / c + 2 * STAGE_K);
+        if (c == 1 || cost < best * 0.98) { best = cost; s = c; }
+    }
+    const char* e = getenv("SVTAD_TC_WGRAD_SPLITS");
+    if (e != nullptr && *e && atoi(e) > 0) s = atoi(e) < max_by_rows ? atoi(e) : max_by_rows;
     long tps = ((n + s - 1) / s + STAGE_K - 1) / STAGE_K * STAGE_K;
     pl.tokens_per_split = tps;
     pl.splits = (int)((n + tps - 1) / tps);
@@ -645,13 +715,13 @@ static int launch_wgrad_tc(const void* gy, const void* x, const int32_t* nbr, fl
                            int cin, int cout, int kk, int tpb, int dtype, const WgradPlan& pl,
                            cudaStream_t s) {
     int nstage = stages_for(BN, 0);
-    size_t smem = 1024 + (size_t)nstage * (A_TILE_BYTES + BN * 128) + sizeof(TcSmemTail);
+    size_t smem = 1024 + (size_t)nstage * (A_TILE_BYTES + b_tile_bytes_for(BN)) + sizeof(TcSmemTail);
     auto kern = wgrad_tc_kernel<BN>;
     SV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)(pl.n_pairs * pl.n_nblk), (unsigned)pl.splits);
     kern<<<grid, TC_THREADS, smem, s>>>((const uint16_t*)gy, (const uint16_t*)x, nbr, ws, (long)n, cin,
                                         cout, kk, tpb, pl.tokens_per_split, pl.n_nblk, nstage,
-                                        dtype == SVTAD_F16 ? 1 : 0);
+                                        dtype == SVTAD_F16 ? 1 : 0, writer_fence_mode() ? 1 : 0);
     SV_LAUNCH_CHECK("wgrad_tc_kernel");
     return SVTAD_OK;
 }

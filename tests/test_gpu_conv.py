@@ -86,7 +86,7 @@ def test_config2_bf16_fwd_bwd_full_size(keep, path, monkeypatch):
     _check_all(table, x, w, b, gy, outs, 2e-2)
 
 
-@pytest.mark.parametrize("bn", ["64", "192"])
+@pytest.mark.parametrize("bn", ["64", "96", "192"])
 def test_tc_column_block_variants(bn, monkeypatch):
     monkeypatch.setenv("SVTAD_FORCE_PATH", "tc")
     monkeypatch.setenv("SVTAD_TC_BN", bn)
@@ -217,6 +217,28 @@ def test_empty_input_and_all_pruned_rows():
     x, w, b, gy = make_conv_inputs(n, 64, 64, 3, torch.bfloat16, 1, bias="random")
     y = ops.conv_fwd(x.cuda(), table.cuda(), w.cuda(), b.cuda())
     assert torch.equal(y.cpu(), b.expand(n, -1).contiguous())
+
+
+def test_tensor_core_pipeline_is_race_free(monkeypatch):
+    """The tensor-core kernels are deterministic, so any hazard between the copy engine's writes
+    and the MMA's reads would show as a run-to-run difference.  40 repeats, bitwise equal."""
+    monkeypatch.setenv("SVTAD_FORCE_PATH", "tc")
+    ops = _ops()
+    _, _, table = make_table(2, 80, 14, 14, 0.3, 3, 77)
+    n = table.shape[0]
+    x, w, b, gy = make_conv_inputs(n, 192, 192, 3, torch.bfloat16, 77, bias="random")
+    tc, xc, wc, bc, gc = (t.cuda() for t in (table, x, w, b, gy))
+    first = None
+    for _ in range(40):
+        cur = (ops.conv_fwd(xc, tc, wc, bc), ops.conv_dgrad(gc, tc, wc, assume_symmetric=True),
+               ops.conv_wgrad(gc, xc, tc, 9)[0])
+        if first is None:
+            first = cur
+        else:
+            for u, v in zip(first, cur):
+                assert torch.equal(u, v)
+    # and the result is the right one
+    assert oconv.rel_err(f32np(first[0]), oconv.fwd(f32np(x), table.numpy(), f32np(w), f32np(b))) < 2e-2
 
 
 def test_determinism_of_backward():
