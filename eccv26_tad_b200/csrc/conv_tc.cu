@@ -18,149 +18,14 @@
 // reduce kernel) and the atomic backward kernels opentad/models/bricks/2d_sparse_v3.cu:656-745.
 #include <cstdlib>
 
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace svtad {
 
 __device__ int g_tc_error = 0;
 
 constexpr int TC_THREADS = 288;        // 4 A-producer warps, 4 B-producer warps, 1 MMA warp
-constexpr int TILE_M = 128;
-constexpr int STAGE_K = 64;            // 64 x 16-bit = one 128-byte swizzle row
-constexpr int A_TILE_BYTES = TILE_M * 128;
 constexpr int LAG = 2;                 // writer-fence protocol only: cp.async groups in flight per thread
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000ll;   // about two seconds
-
-// ---------------------------------------------------------------------------------------------
-// PTX wrappers
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait.  Returns false when the CTA is aborting (this or another wait ran out of time).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* s_abort, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (uint32_t spin = 1;; ++spin) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 31u) == 0u) {
-            if (*s_abort) return false;
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-                *s_abort = 1;
-                atomicCAS(&g_tc_error, 0, code);
-                return false;
-            }
-        }
-    }
-}
-__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-// Arrival on `bar` that fires when all cp.async copies issued so far by this thread have landed; the
-// barrier's expected count already includes it (.noinc), so the issuing thread never blocks.
-__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
-    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t slot_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor, 128-byte swizzle (layout code 2), descriptor version 1.
-// K-major operand:  rows at 128 B, 8-row groups `sbo` apart, `lbo` unused (0).
-// MN-major operand: 64-element (128 B) runs along M/N, `sbo` between 8-row groups along K,
-//                   `lbo` between successive 64-element blocks along M/N.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
-    d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16;
-    d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32;
-    d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
-    return d;
-}
-// Instruction descriptor of tcgen05.mma kind::f16: fp32 accumulate, A/B format (0 = f16, 1 = bf16),
-// operand majors (0 = K-major, 1 = MN-major), N >> 3 at bit 17, M >> 4 at bit 24.
-__host__ __device__ constexpr uint32_t make_idesc(int fmt, int a_mn_major, int b_mn_major, int m, int n) {
-    return (1u << 4) | (static_cast<uint32_t>(fmt) << 7) | (static_cast<uint32_t>(fmt) << 10) |
-           (static_cast<uint32_t>(a_mn_major) << 15) | (static_cast<uint32_t>(b_mn_major) << 16) |
-           (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
-}
-
-__device__ __forceinline__ uint32_t pack2(float lo, float hi, bool fp16) {
-    if (fp16) {
-        __half2 h = __floats2half2_rn(lo, hi);
-        return *reinterpret_cast<uint32_t*>(&h);
-    }
-    __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&b);
-}
-__device__ __forceinline__ float widen(uint16_t v, bool fp16) {
-    if (fp16) return __half2float(__ushort_as_half(v));
-    return __uint_as_float(static_cast<uint32_t>(v) << 16);
-}
-
-// bytes of one B stage: MN-major tiles are whole 64-column blocks of 8 KB, K-major tiles BN rows of 128 B
-constexpr int b_tile_bytes_for(int bn) { return ((bn + 63) / 64) * 8192; }
-constexpr int tmem_cols_for(int bn) { return bn <= 32 ? 32 : bn <= 64 ? 64 : bn <= 128 ? 128 : 256; }
 
 struct TcSmemTail {            // lives after the stage ring in dynamic shared memory
     uint64_t full[8];
@@ -179,7 +44,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 conv_tc_kernel(const uint16_t* __restrict__ a, const int32_t* __restrict__ nbr,
                const uint16_t* __restrict__ w, const uint16_t* __restrict__ bias,
                uint16_t* __restrict__ out, const int32_t* __restrict__ status, long n, int cred,
-               int cn, int cin, int cout, int kk, int tpb, int nstage, int fp16, int writer_fence) {
+               int cn, int cin, int cout, int kk, int tpb, int nstage, int fp16, int writer_fence,
+               int* __restrict__ err, int dbg) {
     if (DGRAD && status != nullptr && (__ldg(status) & SVTAD_TABLE_ASYMMETRIC)) return;
     constexpr int B_TILE_BYTES = b_tile_bytes_for(BN);
     constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
@@ -248,11 +114,13 @@ conv_tc_kernel(const uint16_t* __restrict__ a, const int32_t* __restrict__ nbr,
             const uint16_t* wk = w + (long)wtap * cin * cout;
             for (int kc = 0; kc < kchunks; ++kc, ++it) {
                 const int s = it % nstage;
-                if (!mbar_wait(smem_u32(&tail->empty[s]), ((it / nstage) & 1) ^ 1, s_abort, 1)) { alive = false; break; }
+                if (!mbar_wait(smem_u32(&tail->empty[s]), ((it / nstage) & 1) ^ 1, s_abort, err, 1)) { alive = false; break; }
                 const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
                 const uint32_t b_tile = a_tile + A_TILE_BYTES;
                 const int c0 = kc * STAGE_K;
-                if (warp < 4) {
+                if (dbg & 1) {
+                    // timing experiment: no copies
+                } else if (warp < 4) {
                     // A: 128 rows x 8 chunks of 16 B; 8 consecutive threads cover one row's 128 B
                     const int sub = pt & 7, rbase = pt >> 3;
                     const uint32_t dst0 = a_tile + rbase * 128 + ((sub ^ (rbase & 7)) << 4);
@@ -307,7 +175,7 @@ conv_tc_kernel(const uint16_t* __restrict__ a, const int32_t* __restrict__ nbr,
 
         // ------------------------------------------------------------------ epilogue
         bool have = alive;
-        if (have && total_stages > 0) have = mbar_wait(smem_u32(&tail->accum), 0, s_abort, 3);
+        if (have && total_stages > 0) have = mbar_wait(smem_u32(&tail->accum), 0, s_abort, err, 3);
         tc_fence_after();
         if (have) {
             const int q = warp & 3, hsel = warp >> 2;
@@ -347,7 +215,7 @@ conv_tc_kernel(const uint16_t* __restrict__ a, const int32_t* __restrict__ nbr,
         bool alive = true;
         for (int it = 0; it < total_stages; ++it) {
             const int s = it % nstage;
-            if (!mbar_wait(smem_u32(&tail->full[s]), (it / nstage) & 1, s_abort, 2)) { alive = false; break; }
+            if (!mbar_wait(smem_u32(&tail->full[s]), (it / nstage) & 1, s_abort, err, 2)) { alive = false; break; }
             fence_proxy_async();   // cp.async (generic proxy) writes -> tcgen05.mma (async proxy) reads
             tc_fence_after();
             const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
@@ -357,7 +225,7 @@ conv_tc_kernel(const uint16_t* __restrict__ a, const int32_t* __restrict__ nbr,
                 uint64_t ad = make_smem_desc(a_tile + ks * 32, 0, 1024);
                 uint64_t bd = DGRAD ? make_smem_desc(b_tile + ks * 32, 0, 1024)
                                     : make_smem_desc(b_tile + ks * 2048, 8192, 1024);
-                umma_f16(tmem_base, ad, bd, idesc, (it | ks) != 0 ? 1u : 0u);
+                if (!(dbg & 2)) umma_f16(tmem_base, ad, bd, idesc, (it | ks) != 0 ? 1u : 0u);
             }
             umma_commit(smem_u32(&tail->empty[s]));
         }
@@ -381,7 +249,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 wgrad_tc_kernel(const uint16_t* __restrict__ gy, const uint16_t* __restrict__ x,
                 const int32_t* __restrict__ nbr, float* __restrict__ ws, long n, int cin, int cout,
                 int kk, int tpb, long tokens_per_split, int n_nblk, int nstage, int fp16,
-                int writer_fence) {
+                int writer_fence, int* __restrict__ err) {
     constexpr int B_TILE_BYTES = b_tile_bytes_for(BN);
     constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
     constexpr int TM_COLS = tmem_cols_for(BN);
@@ -456,7 +324,7 @@ wgrad_tc_kernel(const uint16_t* __restrict__ gy, const uint16_t* __restrict__ x,
             for (int it = 0; it < total_stages; ++it) {
                 const int s = it % nstage;
                 if (it + 1 < total_stages) fetch(it + 1, nxt);
-                if (!mbar_wait(smem_u32(&tail->empty[s]), ((it / nstage) & 1) ^ 1, s_abort, 11)) { alive = false; break; }
+                if (!mbar_wait(smem_u32(&tail->empty[s]), ((it / nstage) & 1) ^ 1, s_abort, err, 11)) { alive = false; break; }
                 const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
                 const uint32_t dst0 = a_tile + rbase * 128 + ((sub ^ (rbase & 7)) << 4);
 #pragma unroll
@@ -483,7 +351,7 @@ wgrad_tc_kernel(const uint16_t* __restrict__ gy, const uint16_t* __restrict__ x,
             // B: 64 token rows x BN columns of gy, 64-column blocks 8 KB apart
             for (int it = 0; it < total_stages; ++it) {
                 const int s = it % nstage;
-                if (!mbar_wait(smem_u32(&tail->empty[s]), ((it / nstage) & 1) ^ 1, s_abort, 12)) { alive = false; break; }
+                if (!mbar_wait(smem_u32(&tail->empty[s]), ((it / nstage) & 1) ^ 1, s_abort, err, 12)) { alive = false; break; }
                 const uint32_t b_tile = stage_base + (uint32_t)s * STAGE_BYTES + A_TILE_BYTES;
                 const long i0 = i_begin + (long)it * STAGE_K;
 #pragma unroll
@@ -519,7 +387,7 @@ wgrad_tc_kernel(const uint16_t* __restrict__ gy, const uint16_t* __restrict__ x,
 
         // epilogue: fp32 partial tile -> workspace[split][(tap, ci)][co]
         bool have = alive;
-        if (have && total_stages > 0) have = mbar_wait(smem_u32(&tail->accum), 0, s_abort, 13);
+        if (have && total_stages > 0) have = mbar_wait(smem_u32(&tail->accum), 0, s_abort, err, 13);
         tc_fence_after();
         if (have) {
             const int q = warp & 3, hsel = warp >> 2;
@@ -548,7 +416,7 @@ wgrad_tc_kernel(const uint16_t* __restrict__ gy, const uint16_t* __restrict__ x,
         bool alive = true;
         for (int it = 0; it < total_stages; ++it) {
             const int s = it % nstage;
-            if (!mbar_wait(smem_u32(&tail->full[s]), (it / nstage) & 1, s_abort, 14)) { alive = false; break; }
+            if (!mbar_wait(smem_u32(&tail->full[s]), (it / nstage) & 1, s_abort, err, 14)) { alive = false; break; }
             fence_proxy_async();
             tc_fence_after();
             const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
@@ -578,6 +446,20 @@ wgrad_tc_kernel(const uint16_t* __restrict__ gy, const uint16_t* __restrict__ x,
 // ---------------------------------------------------------------------------------------------
 constexpr size_t SMEM_LIMIT = 227 * 1024;
 
+int* tc_error_ptr() {
+    static thread_local int cached_dev = -1;
+    static thread_local int* cached = nullptr;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    if (dev != cached_dev) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_tc_error) != cudaSuccess) return nullptr;
+        cached = static_cast<int*>(p);
+        cached_dev = dev;
+    }
+    return cached;
+}
+
 static int num_sms() {
     static int cached = 0;
     if (cached == 0) {
@@ -589,6 +471,13 @@ static int num_sms() {
             cached = 148;
     }
     return cached;
+}
+
+// Operand feed of the tensor-core kernels: "tma" (conv_tc_tma.cu) or "cpasync" (this file).
+static bool use_tma() {
+    const char* e = getenv("SVTAD_TC_IMPL");
+    if (e != nullptr && *e) return e[0] == 't';
+    return true;
 }
 
 static bool writer_fence_mode() {
@@ -649,7 +538,8 @@ static int launch_conv_tc(const ConvArgs& p, const int32_t* status, cudaStream_t
     kern<<<grid, TC_THREADS, smem, s>>>((const uint16_t*)p.a, p.nbr, (const uint16_t*)p.w,
                                         (const uint16_t*)p.bias, (uint16_t*)p.out, status, (long)p.n,
                                         cred, cn, p.cin, p.cout, p.kk, p.tpb, nstage,
-                                        p.dtype == SVTAD_F16 ? 1 : 0, writer_fence_mode() ? 1 : 0);
+                                        p.dtype == SVTAD_F16 ? 1 : 0, writer_fence_mode() ? 1 : 0, tc_error_ptr(),
+                                        getenv("SVTAD_TC_DEBUG") ? atoi(getenv("SVTAD_TC_DEBUG")) : 0);
     SV_LAUNCH_CHECK("conv_tc_kernel");
     return SVTAD_OK;
 }
@@ -668,8 +558,12 @@ static int dispatch_conv_tc(const ConvArgs& p, const int32_t* status, cudaStream
     return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core conv: no column block for width %d", cn);
 }
 
-int tc_fwd(const ConvArgs& p, cudaStream_t s) { return dispatch_conv_tc<false>(p, nullptr, s); }
-int tc_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s) { return dispatch_conv_tc<true>(p, status, s); }
+int tc_fwd(const ConvArgs& p, cudaStream_t s) {
+    return use_tma() ? tma_fwd(p, s) : dispatch_conv_tc<false>(p, nullptr, s);
+}
+int tc_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s) {
+    return use_tma() ? tma_dgrad(p, status, s) : dispatch_conv_tc<true>(p, status, s);
+}
 
 struct WgradPlan {
     int bn, n_nblk, n_pairs, splits;
@@ -703,11 +597,16 @@ static WgradPlan wgrad_plan(int64_t n, int cin, int cout, int kk) {
     return pl;
 }
 
-size_t tc_wgrad_ws_bytes(int64_t n, int cin, int cout, int kk) {
+static size_t cpasync_wgrad_ws_bytes(int64_t n, int cin, int cout, int kk) {
     WgradPlan pl = wgrad_plan(n, cin, cout, kk);
     size_t w = (size_t)pl.splits * kk * cin * cout * sizeof(float);
     size_t b = (size_t)bias_splits_for(n) * cout * sizeof(float);
     return align_up(w, 256) + align_up(b, 256);
+}
+
+size_t tc_wgrad_ws_bytes(int64_t n, int cin, int cout, int kk) {
+    size_t a = cpasync_wgrad_ws_bytes(n, cin, cout, kk), b = tma_wgrad_ws_bytes(n, cin, cout, kk);
+    return a > b ? a : b;
 }
 
 template <int BN>
@@ -721,14 +620,15 @@ static int launch_wgrad_tc(const void* gy, const void* x, const int32_t* nbr, fl
     dim3 grid((unsigned)(pl.n_pairs * pl.n_nblk), (unsigned)pl.splits);
     kern<<<grid, TC_THREADS, smem, s>>>((const uint16_t*)gy, (const uint16_t*)x, nbr, ws, (long)n, cin,
                                         cout, kk, tpb, pl.tokens_per_split, pl.n_nblk, nstage,
-                                        dtype == SVTAD_F16 ? 1 : 0, writer_fence_mode() ? 1 : 0);
+                                        dtype == SVTAD_F16 ? 1 : 0, writer_fence_mode() ? 1 : 0, tc_error_ptr());
     SV_LAUNCH_CHECK("wgrad_tc_kernel");
     return SVTAD_OK;
 }
 
 int tc_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw, void* gb, int64_t n, int cin,
              int cout, int kk, int tpb, int dtype, void* ws, size_t ws_bytes, cudaStream_t s) {
-    size_t need = tc_wgrad_ws_bytes(n, cin, cout, kk);
+    if (use_tma()) return tma_wgrad(gy, x, nbr, gw, gb, n, cin, cout, kk, tpb, dtype, ws, ws_bytes, s);
+    size_t need = cpasync_wgrad_ws_bytes(n, cin, cout, kk);
     if (ws_bytes < need)
         return set_error(SVTAD_ERR_WORKSPACE, "svtad_conv_wgrad: workspace %zu < %zu bytes", ws_bytes, need);
     WgradPlan pl = wgrad_plan(n, cin, cout, kk);
