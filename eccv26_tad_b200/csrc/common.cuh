@@ -70,13 +70,15 @@ int tc_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw, void* 
 size_t tc_wgrad_ws_bytes(int64_t n, int cin, int cout, int kk);
 int tc_read_error(int32_t* code_out);
 
-// TMA-fed tcgen05 kernels (conv_tc_tma.cu)
-int tma_fwd(const ConvArgs& p, cudaStream_t s);
-int tma_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s);
-int tma_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw, void* gb, int64_t n,
-              int cin, int cout, int kk, int tpb, int dtype, void* ws, size_t ws_bytes,
-              cudaStream_t s);
-size_t tma_wgrad_ws_bytes(int64_t n, int cin, int cout, int kk);
+// the two tensor-core kernel families behind tc_* (conv_tc_hybrid.cu, conv_tc_gather4.cu)
+#define SV_DECLARE_TC_FAMILY(prefix)                                                                        \
+    int prefix##_fwd(const ConvArgs& p, cudaStream_t s);                                                    \
+    int prefix##_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s);                           \
+    int prefix##_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw, void* gb, int64_t n,    \
+                       int cin, int cout, int kk, int tpb, int dtype, void* ws, size_t ws_bytes,            \
+                       cudaStream_t s);
+SV_DECLARE_TC_FAMILY(hybrid)
+SV_DECLARE_TC_FAMILY(gather4)
 
 #ifdef __CUDACC__
 // ---- device helpers ----

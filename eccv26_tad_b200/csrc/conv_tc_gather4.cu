@@ -1,7 +1,8 @@
-// TMA-fed tcgen05 SparseConv2D kernels (16-bit tensors, fp32 accumulate in tensor memory).
+// All-TMA variant of the tcgen05 SparseConv2D kernels (selected with SVTAD_TC_IMPL=gather4).
 //
-// Same math and tile shapes as conv_tc.cu, but the operands reach shared memory through the
-// tensor-memory-accelerator instead of per-thread copies:
+// Same math and tile shapes as conv_tc_hybrid.cu, but every operand reaches shared memory through the
+// tensor-memory-accelerator.  Measured slower than the hybrid feed on B200 (one gather4 moves only
+// 512 bytes), kept as a validated alternative:
 //   * gathered rows (x for forward / wgrad, gy for dgrad): cp.async.bulk.tensor tile::gather4 - one
 //     instruction fetches four arbitrary rows x 64 channels and writes them 128-byte-swizzled; a row
 //     index past the end of the tensor reads as zeros, which is how -1 table entries are served;
@@ -10,8 +11,6 @@
 // drain the accumulator.  Forward / dgrad CTAs are persistent over output tiles with two accumulators
 // in tensor memory so that a tile's epilogue overlaps the next tile's main loop.  No TMA load here
 // uses cluster multicast.  Every mbarrier wait is bounded (see tc_common.cuh).
-#include <cuda.h>
-
 #include <cstdlib>
 
 #include "tc_common.cuh"
@@ -19,45 +18,6 @@
 namespace svtad {
 
 constexpr int TMA_THREADS = 192;   // warp 0 producer, warp 1 MMA + TMEM owner, warps 2-5 epilogue
-
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, int x, int r0, int r1,
-                                            int r2, int r3, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
-                                            uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
-__device__ __forceinline__ void named_bar_sync(int id, int count) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-
-struct alignas(16) TmaTail {   // 16-byte multiple: the table buffers behind it are filled by 16-byte copies
-    uint64_t full[8];
-    uint64_t empty[8];
-    uint64_t accum_full[2];
-    uint64_t accum_empty[2];
-    uint32_t tmem_slot;
-    int abort_flag;
-};
-
-constexpr int tmem_cols2_for(int bn) { return 2 * bn <= 64 ? 64 : 2 * bn <= 128 ? 128 : 2 * bn <= 256 ? 256 : 512; }
 
 // ---------------------------------------------------------------------------------------------
 // forward / dgrad, persistent over (row tile, column block)
@@ -419,116 +379,9 @@ wgrad_tma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     }
 }
 
-// fixed-order reduction of the per-split partials (4 elements per thread), one rounding
-__global__ void __launch_bounds__(256)
-wgrad_reduce4_kernel(const float* __restrict__ ws_w, int splits, const float* __restrict__ ws_b, int splits_b,
-                     uint16_t* __restrict__ gw, uint16_t* __restrict__ gb, long n_w, int cout, int fp16) {
-    long e = (blockIdx.x * (long)blockDim.x + threadIdx.x) * 4;
-    const float* src;
-    uint16_t* dst;
-    long stride;
-    int cnt;
-    if (e < n_w) {
-        src = ws_w + e; dst = gw + e; stride = n_w; cnt = splits;
-    } else if (gb != nullptr && e - n_w < cout) {
-        src = ws_b + (e - n_w); dst = gb + (e - n_w); stride = cout; cnt = splits_b;
-    } else {
-        return;
-    }
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < cnt; ++s) {
-        float4 v = __ldcg(reinterpret_cast<const float4*>(src + (long)s * stride));
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-    }
-    uint2 o;
-    o.x = pack2(acc.x, acc.y, fp16 != 0);
-    o.y = pack2(acc.z, acc.w, fp16 != 0);
-    *reinterpret_cast<uint2*>(dst) = o;
-}
-
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
-    return fn;
-}
-
-// 16-bit tensor map, 128-byte swizzle, zero fill outside the tensor
-static int make_map(CUtensorMap* map, int rank, const void* base, const uint64_t* dims, const uint32_t* box,
-                    int fp16) {
-    EncodeTiledFn fn = encode_fn();
-    if (fn == nullptr) return set_error(SVTAD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    // the driver call needs this thread to hold the device's context (autograd worker threads may not yet)
-    static thread_local bool ctx_ready = false;
-    if (!ctx_ready) {
-        SV_CUDA(cudaFree(nullptr));
-        ctx_ready = true;
-    }
-    cuuint64_t gdim[3], gstride[2];
-    cuuint32_t bx[3], es[3] = {1, 1, 1};
-    uint64_t stride = 2;
-    for (int i = 0; i < rank; ++i) {
-        gdim[i] = dims[i];
-        bx[i] = box[i];
-        stride *= dims[i];
-        if (i < rank - 1) gstride[i] = stride;
-    }
-    CUresult r = fn(map, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank,
-                    const_cast<void*>(base), gdim, gstride, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return set_error(SVTAD_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
-    return SVTAD_OK;
-}
-
-constexpr size_t TMA_SMEM_LIMIT = 227 * 1024;
-
-static int tma_num_sms() {
-    static int cached = 0;
-    if (cached == 0) {
-        int dev = 0, v = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess &&
-            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
-            cached = v;
-        else
-            cached = 148;
-    }
-    return cached;
-}
-
-static int tma_pick_bn(int cn, long m_tiles) {
-    const int cand[5] = {256, 192, 128, 96, 64};
-    const char* e = getenv("SVTAD_TC_BN");
-    if (e != nullptr && *e) {
-        int v = atoi(e);
-        for (int c : cand)
-            if (v == c && cn % v == 0) return v;
-    }
-    const long sms = tma_num_sms();
-    int best = 0;
-    long best_cost = 0;
-    for (int c : cand) {
-        if (cn % c != 0) continue;
-        long ctas = m_tiles * (cn / c);
-        long waves = (ctas + sms - 1) / sms;
-        long cost = waves * (A_TILE_BYTES + b_tile_bytes_for(c));
-        if (best == 0 || cost < best_cost) { best = c; best_cost = cost; }
-    }
-    return best;
-}
-
 template <int BN, bool DGRAD>
 static int launch_conv_tma(const ConvArgs& p, const int32_t* status, cudaStream_t s) {
     const int cred = DGRAD ? p.cout : p.cin;
@@ -538,18 +391,18 @@ static int launch_conv_tma(const ConvArgs& p, const int32_t* status, cudaStream_
     {
         uint64_t dims[2] = {(uint64_t)cred, (uint64_t)p.n};
         uint32_t box[2] = {64, 1};
-        int rc = make_map(&map_a, 2, p.a, dims, box, fp16);
+        int rc = tc_make_map(&map_a, 2, p.a, dims, box, fp16);
         if (rc) return rc;
     }
     {
         uint64_t dims[3] = {(uint64_t)p.cout, (uint64_t)p.cin, (uint64_t)p.kk};
         uint32_t box[3] = {64, (uint32_t)(DGRAD ? BN : 64), 1};
-        int rc = make_map(&map_w, 3, p.w, dims, box, fp16);
+        int rc = tc_make_map(&map_w, 3, p.w, dims, box, fp16);
         if (rc) return rc;
     }
     const size_t stage = A_TILE_BYTES + b_tile_bytes_for(BN);
     const size_t extra = sizeof(TmaTail) + 2 * (size_t)TILE_M * p.kk * sizeof(int);
-    int nstage = (int)((TMA_SMEM_LIMIT - 1024 - extra) / stage);
+    int nstage = (int)((TC_SMEM_LIMIT - 1024 - extra) / stage);
     if (nstage > 8) nstage = 8;
     if (nstage < 2)
         return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core conv: not enough shared memory for BN=%d kk=%d", BN, p.kk);
@@ -559,7 +412,7 @@ static int launch_conv_tma(const ConvArgs& p, const int32_t* status, cudaStream_
     const int m_tiles = (int)((p.n + TILE_M - 1) / TILE_M);
     const int n_blks = cn / BN;
     long tiles = (long)m_tiles * n_blks;
-    int grid = (int)(tiles < tma_num_sms() ? tiles : tma_num_sms());
+    int grid = (int)(tiles < tc_num_sms() ? tiles : tc_num_sms());
     kern<<<grid, TMA_THREADS, smem, s>>>(map_a, map_w, p.nbr, (const uint16_t*)p.bias, (uint16_t*)p.out, status,
                                          (long)p.n, cred, cn, p.kk, p.tpb, nstage, fp16, m_tiles, n_blks,
                                          tc_error_ptr());
@@ -570,7 +423,7 @@ static int launch_conv_tma(const ConvArgs& p, const int32_t* status, cudaStream_
 template <bool DGRAD>
 static int dispatch_conv_tma(const ConvArgs& p, const int32_t* status, cudaStream_t s) {
     const int cn = DGRAD ? p.cin : p.cout;
-    int bn = tma_pick_bn(cn, (p.n + TILE_M - 1) / TILE_M);
+    int bn = tc_pick_bn(cn, (p.n + TILE_M - 1) / TILE_M);
     switch (bn) {
         case 64: return launch_conv_tma<64, DGRAD>(p, status, s);
         case 96: return launch_conv_tma<96, DGRAD>(p, status, s);
@@ -581,67 +434,27 @@ static int dispatch_conv_tma(const ConvArgs& p, const int32_t* status, cudaStrea
     return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core conv: no column block for width %d", cn);
 }
 
-int tma_fwd(const ConvArgs& p, cudaStream_t s) { return dispatch_conv_tma<false>(p, nullptr, s); }
-int tma_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s) { return dispatch_conv_tma<true>(p, status, s); }
-
-struct TmaWgradPlan {
-    int bn, n_nblk, n_pairs, splits, ones_block;
-    long tokens_per_split;
-};
-
-static TmaWgradPlan tma_wgrad_plan(int64_t n, int cin, int cout, int kk) {
-    TmaWgradPlan pl;
-    pl.bn = (cout <= 256) ? cout : (cout % 256 == 0 ? 256 : (cout % 192 == 0 ? 192 : (cout % 128 == 0 ? 128 : 64)));
-    pl.n_nblk = cout / pl.bn;
-    int nblocks = kk * (cin / 64);
-    pl.n_pairs = (nblocks + 1) / 2;
-    pl.ones_block = nblocks & 1;
-    long ctas = (long)pl.n_pairs * pl.n_nblk;
-    const long sms = tma_num_sms();
-    long max_by_rows = (n + 2 * STAGE_K - 1) / (2 * STAGE_K);
-    if (max_by_rows < 1) max_by_rows = 1;
-    if (max_by_rows > 64) max_by_rows = 64;
-    long s = 1;
-    double best = 0;
-    for (long c = 1; c <= max_by_rows; ++c) {
-        long waves = (ctas * c + sms - 1) / sms;
-        double cost = (double)waves * (double)((n + c - 1) / c + 2 * STAGE_K);
-        if (c == 1 || cost < best * 0.98) { best = cost; s = c; }
-    }
-    const char* e = getenv("SVTAD_TC_WGRAD_SPLITS");
-    if (e != nullptr && *e && atoi(e) > 0) s = atoi(e) < max_by_rows ? atoi(e) : max_by_rows;
-    long tps = ((n + s - 1) / s + STAGE_K - 1) / STAGE_K * STAGE_K;
-    pl.tokens_per_split = tps;
-    pl.splits = (int)((n + tps - 1) / tps);
-    return pl;
-}
-
-size_t tma_wgrad_ws_bytes(int64_t n, int cin, int cout, int kk) {
-    TmaWgradPlan pl = tma_wgrad_plan(n, cin, cout, kk);
-    size_t w = (size_t)pl.splits * kk * cin * cout * sizeof(float);
-    int sb = pl.ones_block ? pl.splits : bias_splits_for(n);
-    size_t b = (size_t)sb * cout * sizeof(float);
-    return align_up(w, 256) + align_up(b, 256);
-}
+int gather4_fwd(const ConvArgs& p, cudaStream_t s) { return dispatch_conv_tma<false>(p, nullptr, s); }
+int gather4_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s) { return dispatch_conv_tma<true>(p, status, s); }
 
 template <int BN>
 static int launch_wgrad_tma(const void* gy, const void* x, const int32_t* nbr, float* ws_w, float* ws_b, int64_t n,
-                            int cin, int cout, int kk, int tpb, int fp16, const TmaWgradPlan& pl, cudaStream_t s) {
+                            int cin, int cout, int kk, int tpb, int fp16, const WgradPlan& pl, cudaStream_t s) {
     CUtensorMap map_x, map_gy;
     {
         uint64_t dims[2] = {(uint64_t)cin, (uint64_t)n};
         uint32_t box[2] = {64, 1};
-        int rc = make_map(&map_x, 2, x, dims, box, fp16);
+        int rc = tc_make_map(&map_x, 2, x, dims, box, fp16);
         if (rc) return rc;
     }
     {
         uint64_t dims[2] = {(uint64_t)cout, (uint64_t)n};
         uint32_t box[2] = {64, 64};
-        int rc = make_map(&map_gy, 2, gy, dims, box, fp16);
+        int rc = tc_make_map(&map_gy, 2, gy, dims, box, fp16);
         if (rc) return rc;
     }
     const size_t stage = A_TILE_BYTES + b_tile_bytes_for(BN);
-    int nstage = (int)((TMA_SMEM_LIMIT - 1024 - sizeof(TmaTail)) / stage);
+    int nstage = (int)((TC_SMEM_LIMIT - 1024 - sizeof(TmaTail)) / stage);
     if (nstage > 8) nstage = 8;
     const size_t smem = 1024 + nstage * stage + sizeof(TmaTail);
     auto kern = wgrad_tma_kernel<BN>;
@@ -654,12 +467,12 @@ static int launch_wgrad_tma(const void* gy, const void* x, const int32_t* nbr, f
     return SVTAD_OK;
 }
 
-int tma_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw, void* gb, int64_t n, int cin, int cout,
+int gather4_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw, void* gb, int64_t n, int cin, int cout,
               int kk, int tpb, int dtype, void* ws, size_t ws_bytes, cudaStream_t s) {
-    size_t need = tma_wgrad_ws_bytes(n, cin, cout, kk);
+    size_t need = tc_wgrad_plan_ws_bytes(n, cin, cout, kk);
     if (ws_bytes < need)
         return set_error(SVTAD_ERR_WORKSPACE, "svtad_conv_wgrad: workspace %zu < %zu bytes", ws_bytes, need);
-    TmaWgradPlan pl = tma_wgrad_plan(n, cin, cout, kk);
+    WgradPlan pl = tc_wgrad_plan(n, cin, cout, kk);
     const int fp16 = dtype == SVTAD_F16 ? 1 : 0;
     const long n_w = (long)kk * cin * cout;
     float* ws_w = static_cast<float*>(ws);
@@ -684,11 +497,7 @@ int tma_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw, void*
             if (rc) return rc;
         }
     }
-    long total4 = (n_w + (gb ? cout : 0) + 3) / 4;
-    wgrad_reduce4_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, s>>>(
-        ws_w, pl.splits, ws_b, splits_b, (uint16_t*)gw, (uint16_t*)gb, n_w, cout, fp16);
-    SV_LAUNCH_CHECK("wgrad_reduce4_kernel");
-    return SVTAD_OK;
+    return tc_wgrad_reduce_launch(ws_w, pl.splits, ws_b, splits_b, gw, gb, n_w, cout, fp16, s);
 }
 
 }  // namespace svtad

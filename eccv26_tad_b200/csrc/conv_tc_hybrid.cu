@@ -1,0 +1,555 @@
+// Default tcgen05 / TMEM SparseConv2D kernels for 16-bit tensors (bf16 / fp16 in, fp32 accumulate).
+//
+//   forward   D[128 rows, BN] += A(K-major: gathered x rows, 64 channels per stage) . B(MN-major: W[k])
+//   dgrad     same kernel, A = gathered gy rows through the table, B = W[KK-1-k] read K-major (i.e.
+//             transposed) - the gather form of the input gradient, valid for symmetric tables
+//   wgrad     D[128 = two 64-channel blocks of (tap, ci), BN] += A(MN-major: gathered x rows, 64 tokens
+//             per stage) . B(MN-major: gy rows); split over tokens, fp32 partials to the workspace;
+//             an all-ones spare block turns the bias gradient into one more row of D
+//
+// Operand feed.  Gathered rows are irregular, so four producer warps copy them with 16-byte cp.async
+// straight into the 128-byte-swizzled layout the UMMA descriptors describe (nothing gathered is ever
+// materialised in HBM); each warp owns every fourth pipeline stage, so a stage costs 32 barrier
+// arrivals instead of one per thread.  Regular tiles (weights, gy) come through TMA, issued by lane 0
+// of the warp that owns the stage.  One elected thread issues tcgen05.mma; four warps drain the
+// accumulator (tcgen05.ld -> +bias -> one rounding -> 16-byte stores).
+//
+// Forward / dgrad CTAs are persistent over (row tile, column block) work items with two accumulators in
+// tensor memory, so a tile's epilogue overlaps the next tile's main loop; the tile's table rows are
+// prefetched into shared memory one tile ahead.  No TMA load uses cluster multicast.  Every mbarrier wait
+// is bounded: when it runs out the CTA records a code in the device error word, stops, frees its tensor
+// memory and returns.
+#include <cstdlib>
+
+#include "tc_common.cuh"
+
+namespace svtad {
+
+constexpr int HY_THREADS = 288;    // warps 0-3 producers, warp 4 MMA + TMEM owner, warps 5-8 epilogue
+constexpr int A_WARPS = 4;
+constexpr int A_THREADS = A_WARPS * 32;
+
+// lane 0 waits (bounded), the whole warp learns the outcome
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* s_abort, int* err, int code,
+                                          int lane) {
+    int ok = 1;
+    if (lane == 0) ok = mbar_wait(bar, parity, s_abort, err, code) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// forward / dgrad
+// ---------------------------------------------------------------------------------------------
+template <int BN, bool DGRAD>
+__global__ void __launch_bounds__(HY_THREADS, 1)
+conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __restrict__ a,
+                   const int32_t* __restrict__ nbr, const uint16_t* __restrict__ bias,
+                   uint16_t* __restrict__ out, const int32_t* __restrict__ status, long n, int cred, int cn,
+                   int kk, int tpb, int nstage, int fp16, int m_tiles, int n_blks, int rotate,
+                   int* __restrict__ err, int dbg) {
+    if (DGRAD && status != nullptr && (__ldg(status) & SVTAD_TABLE_ASYMMETRIC)) return;
+    constexpr int B_TILE_BYTES = b_tile_bytes_for(BN);
+    constexpr int B_TX_BYTES = DGRAD ? BN * 128 : B_TILE_BYTES;
+    constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+    constexpr int TM_COLS = tmem_cols2_for(BN);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    TmaTail* tail = reinterpret_cast<TmaTail*>(smem + (size_t)nstage * STAGE_BYTES);
+    int* s_tab = reinterpret_cast<int*>(tail + 1);                 // [2][TILE_M * kk] table rows of a tile
+    volatile int* s_abort = &tail->abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t stage_base = smem_u32(smem);
+    const int tiles_total = m_tiles * n_blks;
+    const int kchunks = cred / STAGE_K;
+    const int stages_per_tile = kk * kchunks;
+    const int tab_ints = TILE_M * kk;
+
+    if (warp == 4) {
+        tmem_alloc(smem_u32(&tail->tmem_slot), TM_COLS);
+        tmem_relinquish();
+    }
+    if (tid == 0) {
+        for (int s = 0; s < nstage; ++s) {
+            mbar_init(smem_u32(&tail->full[s]), 33);    // 32 copy arrivals + the TMA byte-count arrival
+            mbar_init(smem_u32(&tail->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&tail->accum_full[b]), 1);
+            mbar_init(smem_u32(&tail->accum_empty[b]), 128);
+        }
+        tail->abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_map(&map_w);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tail->tmem_slot;
+
+    if (warp < A_WARPS) {
+        // ------------------------------------------------------------------ producers
+        auto load_table = [&](int tile, int buf) {
+            const long row0 = (long)(tile / n_blks) * TILE_M;
+            const long rows = (n - row0) < TILE_M ? (n - row0) : TILE_M;
+            const int valid_bytes = (int)rows * kk * 4;
+            const char* src = reinterpret_cast<const char*>(nbr + row0 * kk);
+            const uint32_t dst = smem_u32(s_tab + buf * tab_ints);
+            for (int c = tid; c * 16 < tab_ints * 4; c += A_THREADS) {
+                int left = valid_bytes - c * 16;
+                uint32_t nb = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
+                cp_async16(dst + c * 16, nb ? src + c * 16 : src, nb);
+            }
+            cp_async_commit();
+        };
+        const int sub = lane & 7, rg = lane >> 3;
+        bool alive = true;
+        int local = 0;
+        if ((int)blockIdx.x < tiles_total) load_table(blockIdx.x, 0);
+        for (int tile = blockIdx.x; tile < tiles_total; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const long row0 = (long)(tile / n_blks) * TILE_M;
+            const int n0 = (tile % n_blks) * BN;
+            int* tab = s_tab + buf * tab_ints;
+            // this tile's table rows have landed (only table copies are ever committed to a group)
+            cp_async_wait<0>();
+            named_bar_sync(1, A_THREADS);
+            // entries become final row numbers: batch offset folded in, -1 for anything that reads as zero
+            for (int e = tid; e < tab_ints; e += A_THREADS) {
+                int r = e / kk;
+                long i = row0 + r;
+                int raw = tab[e];
+                long jj = (long)raw + (tpb > 0 ? (i / tpb) * (long)tpb : 0);
+                tab[e] = (i < n && raw >= 0 && jj < n) ? (int)jj : -1;
+            }
+            named_bar_sync(1, A_THREADS);
+            if (tile + (int)gridDim.x < tiles_total) load_table(tile + gridDim.x, buf ^ 1);
+            if (!alive) continue;   // keep taking part in the barriers above
+            const int it0 = local * stages_per_tile;
+            // every tile walks the (tap, channel chunk) steps from its own starting point, so that CTAs
+            // running side by side pull different weight tiles out of L2 instead of the same one
+            const int rot = rotate ? (int)(((long)tile * 11) % stages_per_tile) : 0;
+            for (int st = 0; st < stages_per_tile; ++st) {
+                const int it = it0 + st;
+                if ((it & (A_WARPS - 1)) != warp) continue;
+                int sr = st + rot;
+                if (sr >= stages_per_tile) sr -= stages_per_tile;
+                const int k = sr / kchunks, kc = sr - k * kchunks;
+                const int s = it % nstage;
+                if (!warp_wait(smem_u32(&tail->empty[s]), ((it / nstage) & 1) ^ 1, s_abort, err, 41, lane)) { alive = false; break; }
+                const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
+                const uint32_t bar = smem_u32(&tail->full[s]);
+                const int c0 = kc * STAGE_K;
+                if (lane == 0) {
+                    const uint32_t b_tile = a_tile + A_TILE_BYTES;
+                    const int wtap = DGRAD ? (kk - 1 - k) : k;
+                    if (dbg & 4) {
+                        mbar_arrive(bar);            // timing experiment: no weight tile
+                    } else {
+                    mbar_expect_tx(bar, B_TX_BYTES);
+                    if (!DGRAD) {
+#pragma unroll
+                        for (int b = 0; b < B_TILE_BYTES / 8192; ++b)
+                            tma_load_3d(b_tile + b * 8192, &map_w, n0 + b * 64, c0, wtap, bar);
+                    } else {
+                        tma_load_3d(b_tile, &map_w, c0, n0, wtap, bar);
+                    }
+                    }
+                }
+                // A: 128 rows x 8 chunks of 16 B; 8 consecutive lanes cover one row's 128 B
+                const uint16_t* abase = a + c0 + sub * 8;
+                const int* trow = tab + rg * kk + k;
+#pragma unroll 8
+                for (int itr = 0; itr < ((dbg & 1) ? 0 : 32); ++itr) {
+                    const int j = trow[itr * 4 * kk];
+                    const int r7 = ((itr & 1) << 2) | rg;            // (row & 7) for row = itr * 4 + rg
+                    const uint32_t dst = a_tile + (itr * 4 + rg) * 128 + ((sub ^ r7) << 4);
+                    cp_async16(dst, abase + (long)(j < 0 ? 0 : j) * cred, j < 0 ? 0u : 16u);
+                }
+                cp_async_arrive_noinc(bar);
+            }
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+    } else if (warp == 4) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(fp16 ? 0 : 1, 0, DGRAD ? 0 : 1, TILE_M, BN);
+            bool alive = true;
+            int it = 0, local = 0;
+            for (int tile = blockIdx.x; tile < tiles_total && alive; tile += gridDim.x, ++local) {
+                const int buf = local & 1;
+                if (!mbar_wait(smem_u32(&tail->accum_empty[buf]), ((local >> 1) & 1) ^ 1, s_abort, err, 42)) { alive = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int st = 0; st < stages_per_tile; ++st, ++it) {
+                    const int s = it % nstage;
+                    if (!mbar_wait(smem_u32(&tail->full[s]), (it / nstage) & 1, s_abort, err, 43)) { alive = false; break; }
+                    if (!(dbg & 8)) fence_proxy_async();   // cp.async (generic proxy) writes -> tcgen05.mma (async proxy) reads
+                    if (!(dbg & 16)) tc_fence_after();
+                    const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
+                    const uint32_t b_tile = a_tile + A_TILE_BYTES;
+#pragma unroll
+                    for (int ks = 0; ks < STAGE_K / 16; ++ks) {
+                        uint64_t ad = make_smem_desc(a_tile + ks * 32, 0, 1024);
+                        uint64_t bd = DGRAD ? make_smem_desc(b_tile + ks * 32, 0, 1024)
+                                            : make_smem_desc(b_tile + ks * 2048, 8192, 1024);
+                        if (!(dbg & 2)) umma_f16(d_tmem, ad, bd, idesc, (st | ks) != 0 ? 1u : 0u);
+                    }
+                    umma_commit(smem_u32(&tail->empty[s]));
+                }
+                if (alive) umma_commit(smem_u32(&tail->accum_full[buf]));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 5..8)
+        const int q = warp & 3;
+        int local = 0;
+        for (int tile = blockIdx.x; tile < tiles_total; tile += gridDim.x, ++local) {
+            const int buf = local & 1;
+            const long row = (long)(tile / n_blks) * TILE_M + q * 32 + lane;
+            const int n0 = (tile % n_blks) * BN;
+            if (!mbar_wait(smem_u32(&tail->accum_full[buf]), (local >> 1) & 1, s_abort, err, 44)) break;
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int cbase = 0; cbase < BN; cbase += 32) {
+                uint32_t v[32];
+                tmem_ld32(t_addr + cbase, v);
+                tmem_ld_wait();
+                if (row < n) {
+                    uint4* dst = reinterpret_cast<uint4*>(out + row * cn + n0 + cbase);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        float b8[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            b8[e] = (!DGRAD && bias != nullptr) ? widen(__ldg(bias + n0 + cbase + g * 8 + e), fp16 != 0) : 0.f;
+                        uint4 o;
+                        o.x = pack2(__uint_as_float(v[g * 8 + 0]) + b8[0], __uint_as_float(v[g * 8 + 1]) + b8[1], fp16 != 0);
+                        o.y = pack2(__uint_as_float(v[g * 8 + 2]) + b8[2], __uint_as_float(v[g * 8 + 3]) + b8[3], fp16 != 0);
+                        o.z = pack2(__uint_as_float(v[g * 8 + 4]) + b8[4], __uint_as_float(v[g * 8 + 5]) + b8[5], fp16 != 0);
+                        o.w = pack2(__uint_as_float(v[g * 8 + 6]) + b8[6], __uint_as_float(v[g * 8 + 7]) + b8[7], fp16 != 0);
+                        dst[g] = o;
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(smem_u32(&tail->accum_empty[buf]));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// wgrad
+// ---------------------------------------------------------------------------------------------
+template <int BN>
+__global__ void __launch_bounds__(HY_THREADS, 1)
+wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* __restrict__ x,
+                    const int32_t* __restrict__ nbr, float* __restrict__ ws_w, float* __restrict__ ws_b,
+                    long n, int cin, int cout, int kk, int tpb, long tokens_per_split, int n_nblk,
+                    int nstage, int fp16, int ones_block, int rotate, int* __restrict__ err) {
+    constexpr int B_TILE_BYTES = b_tile_bytes_for(BN);
+    constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+    constexpr int TM_COLS = tmem_cols_for(BN);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    TmaTail* tail = reinterpret_cast<TmaTail*>(smem + (size_t)nstage * STAGE_BYTES);
+    int* s_idx = reinterpret_cast<int*>(tail + 1);                 // [A_WARPS][2][TILE_M] gather rows of a stage
+    volatile int* s_abort = &tail->abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int pair = blockIdx.x / n_nblk;
+    const int n0 = (blockIdx.x % n_nblk) * BN;
+    const int cblocks = cin / 64;
+    const int nblocks = kk * cblocks;
+    const long i_begin = (long)blockIdx.y * tokens_per_split;
+    const long i_end = n < i_begin + tokens_per_split ? n : i_begin + tokens_per_split;
+    const int total_stages = i_end > i_begin ? (int)((i_end - i_begin + STAGE_K - 1) / STAGE_K) : 0;
+    const uint32_t stage_base = smem_u32(smem);
+    const bool second_real = pair * 2 + 1 < nblocks;
+    // second block of the last pair when the block count is odd: all ones, so its rows of D are sum_i gy[i,:]
+    const bool ones_here = ones_block && !second_real;
+
+    if (warp == 4) {
+        tmem_alloc(smem_u32(&tail->tmem_slot), TM_COLS);
+        tmem_relinquish();
+    }
+    if (tid == 0) {
+        for (int s = 0; s < nstage; ++s) {
+            mbar_init(smem_u32(&tail->full[s]), 33);
+            mbar_init(smem_u32(&tail->empty[s]), 1);
+        }
+        mbar_init(smem_u32(&tail->accum_full[0]), 1);
+        tail->abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_map(&map_gy);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tail->tmem_slot;
+
+    if (warp < A_WARPS) {
+        // ------------------------------------------------------------------ producers
+        if (!second_real) {
+            // the missing second block of every stage is written once: ones (bias row) or zeros
+            const uint32_t word = ones_here ? (fp16 ? 0x3C003C00u : 0x3F803F80u) : 0u;
+            for (int s = 0; s < nstage; ++s) {
+                uint32_t base = stage_base + (uint32_t)s * STAGE_BYTES + 8192;
+                for (int c = tid; c < 512; c += A_THREADS)
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(base + c * 16), "r"(word) : "memory");
+            }
+            fence_proxy_async();
+            named_bar_sync(1, A_THREADS);
+        }
+        int tap[2], ch0[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            int blk = pair * 2 + h;
+            bool real = blk < nblocks;
+            tap[h] = real ? blk / cblocks : 0;
+            ch0[h] = real ? (blk % cblocks) * 64 : 0;
+        }
+        int* my_idx = s_idx + warp * 2 * TILE_M;
+        // gather rows of stage `sit` for slots lane*4 .. lane*4+3 (slot = block * 64 + token)
+        auto fetch = [&](int sit, int (&dst)[4]) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int slot = lane * 4 + j;
+                const int h = slot >> 6;
+                long i = i_begin + (long)sit * STAGE_K + (slot & 63);
+                int v = -1;
+                if ((h == 0 || second_real) && i < i_end) {
+                    int raw = __ldg(nbr + i * kk + tap[h]);
+                    long jj = (long)raw + (tpb > 0 ? (i / tpb) * (long)tpb : 0);
+                    if (raw >= 0 && jj < n) v = (int)jj;
+                }
+                dst[j] = v;
+            }
+        };
+        const int sub = lane & 7, rg = lane >> 3;
+        // CTAs of different block pairs walk the token range from different starting points (see the
+        // forward kernel); `src_stage` is the 64-token step that pipeline step `it` carries
+        const int rot = (rotate && total_stages > 0) ? (int)(((long)blockIdx.x * 5) % total_stages) : 0;
+        auto src_stage = [&](int it) { int v = it + rot; return v >= total_stages ? v - total_stages : v; };
+        int nxt[4] = {-1, -1, -1, -1};
+        if (warp < total_stages) fetch(src_stage(warp), nxt);
+        int local = 0;
+        for (int it = warp; it < total_stages; it += A_WARPS, ++local) {
+            int* idx = my_idx + (local & 1) * TILE_M;
+            *reinterpret_cast<int4*>(idx + lane * 4) = make_int4(nxt[0], nxt[1], nxt[2], nxt[3]);
+            __syncwarp();
+            if (it + A_WARPS < total_stages) fetch(src_stage(it + A_WARPS), nxt);
+            const int s = it % nstage;
+            if (!warp_wait(smem_u32(&tail->empty[s]), ((it / nstage) & 1) ^ 1, s_abort, err, 51, lane)) break;
+            const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
+            const uint32_t bar = smem_u32(&tail->full[s]);
+            if (lane == 0) {
+                const uint32_t b_tile = a_tile + A_TILE_BYTES;
+                const int i0 = (int)(i_begin + (long)src_stage(it) * STAGE_K);
+                mbar_expect_tx(bar, B_TILE_BYTES);
+#pragma unroll
+                for (int b = 0; b < B_TILE_BYTES / 8192; ++b)
+                    tma_load_2d(b_tile + b * 8192, &map_gy, n0 + b * 64, i0, bar);
+            }
+            const int rows = second_real ? 32 : 16;        // rows 64..127 belong to the second block
+#pragma unroll 8
+            for (int itr = 0; itr < rows; ++itr) {
+                const int r = itr * 4 + rg;
+                const int j = idx[r];
+                const int r7 = ((itr & 1) << 2) | rg;
+                const uint32_t dst = a_tile + r * 128 + ((sub ^ r7) << 4);
+                const uint16_t* src = x + (long)(j < 0 ? 0 : j) * cin + ch0[r >> 6] + sub * 8;
+                cp_async16(dst, src, j < 0 ? 0u : 16u);
+            }
+            cp_async_arrive_noinc(bar);
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+    } else if (warp == 4) {
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(fp16 ? 0 : 1, 1, 1, TILE_M, BN);
+            bool alive = true;
+            for (int it = 0; it < total_stages; ++it) {
+                const int s = it % nstage;
+                if (!mbar_wait(smem_u32(&tail->full[s]), (it / nstage) & 1, s_abort, err, 52)) { alive = false; break; }
+                fence_proxy_async();
+                tc_fence_after();
+                const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
+                const uint32_t b_tile = a_tile + A_TILE_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < STAGE_K / 16; ++ks) {
+                    uint64_t ad = make_smem_desc(a_tile + ks * 2048, 8192, 1024);
+                    uint64_t bd = make_smem_desc(b_tile + ks * 2048, 8192, 1024);
+                    umma_f16(tmem_base, ad, bd, idesc, (it | ks) != 0 ? 1u : 0u);
+                }
+                umma_commit(smem_u32(&tail->empty[s]));
+            }
+            if (alive && total_stages > 0) umma_commit(smem_u32(&tail->accum_full[0]));
+        }
+    } else {
+        // epilogue: fp32 partial tile -> ws_w[split][(tap, ci)][co]; the all-ones block -> ws_b[split][co]
+        bool have = true;
+        if (total_stages > 0) have = mbar_wait(smem_u32(&tail->accum_full[0]), 0, s_abort, err, 53);
+        tc_fence_after();
+        if (have) {
+            const int q = warp & 3;
+            const int blk = pair * 2 + (q >> 1);
+            float* dstrow = nullptr;
+            if (blk < nblocks) {
+                const long grow = (long)(blk / cblocks) * cin + (blk % cblocks) * 64 + (q & 1) * 32 + lane;
+                dstrow = ws_w + ((long)blockIdx.y * kk * cin + grow) * cout + n0;
+            } else if (ones_here && q == 2 && lane == 0 && ws_b != nullptr) {
+                dstrow = ws_b + (long)blockIdx.y * cout + n0;
+            }
+#pragma unroll 1
+            for (int cbase = 0; cbase < BN; cbase += 32) {
+                uint32_t v[32];
+                if (total_stages > 0) {
+                    tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + cbase, v);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) v[j] = 0u;
+                }
+                if (dstrow != nullptr) {
+                    uint4* dst = reinterpret_cast<uint4*>(dstrow + cbase);
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) dst[g] = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+template <int BN, bool DGRAD>
+static int launch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaStream_t s) {
+    const int cred = DGRAD ? p.cout : p.cin;
+    const int cn = DGRAD ? p.cin : p.cout;
+    const int fp16 = p.dtype == SVTAD_F16 ? 1 : 0;
+    CUtensorMap map_w;
+    {
+        uint64_t dims[3] = {(uint64_t)p.cout, (uint64_t)p.cin, (uint64_t)p.kk};
+        uint32_t box[3] = {64, (uint32_t)(DGRAD ? BN : 64), 1};
+        int rc = tc_make_map(&map_w, 3, p.w, dims, box, fp16);
+        if (rc) return rc;
+    }
+    const size_t stage = A_TILE_BYTES + b_tile_bytes_for(BN);
+    const size_t extra = sizeof(TmaTail) + 2 * (size_t)TILE_M * p.kk * sizeof(int);
+    int nstage = (int)((TC_SMEM_LIMIT - 1024 - extra) / stage);
+    if (nstage > 8) nstage = 8;
+    if (getenv("SVTAD_TC_NSTAGE") && atoi(getenv("SVTAD_TC_NSTAGE")) >= 2 && atoi(getenv("SVTAD_TC_NSTAGE")) < nstage)
+        nstage = atoi(getenv("SVTAD_TC_NSTAGE"));
+    if (nstage < 2)
+        return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core conv: not enough shared memory for BN=%d kk=%d", BN, p.kk);
+    const size_t smem = 1024 + nstage * stage + extra;
+    auto kern = conv_hybrid_kernel<BN, DGRAD>;
+    SV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int m_tiles = (int)((p.n + TILE_M - 1) / TILE_M);
+    const int n_blks = cn / BN;
+    long tiles = (long)m_tiles * n_blks;
+    int grid = (int)(tiles < tc_num_sms() ? tiles : tc_num_sms());
+    kern<<<grid, HY_THREADS, smem, s>>>(map_w, (const uint16_t*)p.a, p.nbr, (const uint16_t*)p.bias,
+                                        (uint16_t*)p.out, status, (long)p.n, cred, cn, p.kk, p.tpb, nstage, fp16,
+                                        m_tiles, n_blks, tc_rotate_enabled() ? 1 : 0, tc_error_ptr(),
+                                        getenv("SVTAD_TC_DEBUG") ? atoi(getenv("SVTAD_TC_DEBUG")) : 0);
+    SV_LAUNCH_CHECK("conv_hybrid_kernel");
+    return SVTAD_OK;
+}
+
+template <bool DGRAD>
+static int dispatch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaStream_t s) {
+    const int cn = DGRAD ? p.cin : p.cout;
+    int bn = tc_pick_bn(cn, (p.n + TILE_M - 1) / TILE_M);
+    switch (bn) {
+        case 64: return launch_conv_hybrid<64, DGRAD>(p, status, s);
+        case 96: return launch_conv_hybrid<96, DGRAD>(p, status, s);
+        case 128: return launch_conv_hybrid<128, DGRAD>(p, status, s);
+        case 192: return launch_conv_hybrid<192, DGRAD>(p, status, s);
+        case 256: return launch_conv_hybrid<256, DGRAD>(p, status, s);
+    }
+    return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core conv: no column block for width %d", cn);
+}
+
+int hybrid_fwd(const ConvArgs& p, cudaStream_t s) { return dispatch_conv_hybrid<false>(p, nullptr, s); }
+int hybrid_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s) { return dispatch_conv_hybrid<true>(p, status, s); }
+
+template <int BN>
+static int launch_wgrad_hybrid(const void* gy, const void* x, const int32_t* nbr, float* ws_w, float* ws_b,
+                               int64_t n, int cin, int cout, int kk, int tpb, int fp16, const WgradPlan& pl,
+                               cudaStream_t s) {
+    CUtensorMap map_gy;
+    {
+        uint64_t dims[2] = {(uint64_t)cout, (uint64_t)n};
+        uint32_t box[2] = {64, 64};
+        int rc = tc_make_map(&map_gy, 2, gy, dims, box, fp16);
+        if (rc) return rc;
+    }
+    const size_t stage = A_TILE_BYTES + b_tile_bytes_for(BN);
+    const size_t extra = sizeof(TmaTail) + (size_t)A_WARPS * 2 * TILE_M * sizeof(int);
+    int nstage = (int)((TC_SMEM_LIMIT - 1024 - extra) / stage);
+    if (nstage > 8) nstage = 8;
+    const size_t smem = 1024 + nstage * stage + extra;
+    auto kern = wgrad_hybrid_kernel<BN>;
+    SV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)(pl.n_pairs * pl.n_nblk), (unsigned)pl.splits);
+    kern<<<grid, HY_THREADS, smem, s>>>(map_gy, (const uint16_t*)x, nbr, ws_w, ws_b, (long)n, cin, cout, kk, tpb,
+                                        pl.tokens_per_split, pl.n_nblk, nstage, fp16, pl.ones_block,
+                                        tc_rotate_enabled() ? 1 : 0, tc_error_ptr());
+    SV_LAUNCH_CHECK("wgrad_hybrid_kernel");
+    return SVTAD_OK;
+}
+
+int hybrid_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw, void* gb, int64_t n, int cin, int cout,
+                 int kk, int tpb, int dtype, void* ws, size_t ws_bytes, cudaStream_t s) {
+    size_t need = tc_wgrad_plan_ws_bytes(n, cin, cout, kk);
+    if (ws_bytes < need)
+        return set_error(SVTAD_ERR_WORKSPACE, "svtad_conv_wgrad: workspace %zu < %zu bytes", ws_bytes, need);
+    WgradPlan pl = tc_wgrad_plan(n, cin, cout, kk);
+    const int fp16 = dtype == SVTAD_F16 ? 1 : 0;
+    const long n_w = (long)kk * cin * cout;
+    float* ws_w = static_cast<float*>(ws);
+    float* ws_b = reinterpret_cast<float*>(static_cast<char*>(ws) + align_up((size_t)pl.splits * n_w * sizeof(float), 256));
+    const bool bias_in_kernel = gb != nullptr && pl.ones_block;
+    float* kb = bias_in_kernel ? ws_b : nullptr;
+    int rc;
+    switch (pl.bn) {
+        case 64: rc = launch_wgrad_hybrid<64>(gy, x, nbr, ws_w, kb, n, cin, cout, kk, tpb, fp16, pl, s); break;
+        case 128: rc = launch_wgrad_hybrid<128>(gy, x, nbr, ws_w, kb, n, cin, cout, kk, tpb, fp16, pl, s); break;
+        case 192: rc = launch_wgrad_hybrid<192>(gy, x, nbr, ws_w, kb, n, cin, cout, kk, tpb, fp16, pl, s); break;
+        case 256: rc = launch_wgrad_hybrid<256>(gy, x, nbr, ws_w, kb, n, cin, cout, kk, tpb, fp16, pl, s); break;
+        default: return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core wgrad: no column block for width %d", cout);
+    }
+    if (rc) return rc;
+    int splits_b = 0;
+    if (gb != nullptr) {
+        if (bias_in_kernel) {
+            splits_b = pl.splits;
+        } else {
+            splits_b = bias_splits_for(n);
+            rc = bias_partial_launch(gy, ws_b, n, cout, dtype, splits_b, s);
+            if (rc) return rc;
+        }
+    }
+    return tc_wgrad_reduce_launch(ws_w, pl.splits, ws_b, splits_b, gw, gb, n_w, cout, fp16, s);
+}
+
+}  // namespace svtad

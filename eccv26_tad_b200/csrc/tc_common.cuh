@@ -1,5 +1,7 @@
 // PTX wrappers and descriptor builders shared by the tcgen05 kernels.
 #pragma once
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace svtad {
@@ -143,5 +145,63 @@ __device__ __forceinline__ float widen(uint16_t v, bool fp16) {
 constexpr int b_tile_bytes_for(int bn) { return ((bn + 63) / 64) * 8192; }
 constexpr int tmem_cols_for(int bn) { return bn <= 32 ? 32 : bn <= 64 ? 64 : bn <= 128 ? 128 : 256; }
 
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, int x, int r0, int r1,
+                                            int r2, int r3, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes "
+        "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+struct alignas(16) TmaTail {   // 16-byte multiple: the table buffers behind it are filled by 16-byte copies
+    uint64_t full[8];
+    uint64_t empty[8];
+    uint64_t accum_full[2];
+    uint64_t accum_empty[2];
+    uint32_t tmem_slot;
+    int abort_flag;
+};
+
+constexpr int tmem_cols2_for(int bn) { return 2 * bn <= 64 ? 64 : 2 * bn <= 128 ? 128 : 2 * bn <= 256 ? 256 : 512; }
+
+
+// ---- host helpers shared by the tensor-core translation units (defined in conv_tc.cu) ----
+constexpr size_t TC_SMEM_LIMIT = 227 * 1024;
+int tc_num_sms();
+bool tc_rotate_enabled();   // SVTAD_TC_ROTATE=0 makes every CTA walk its K steps in the same order
+// 16-bit tensor map with 128-byte swizzle and zero fill outside the tensor; dims[0] is the contiguous one
+int tc_make_map(CUtensorMap* map, int rank, const void* base, const uint64_t* dims, const uint32_t* box, int fp16);
+// column-block width of a forward / dgrad CTA for an output of `cn` columns and `m_tiles` row tiles
+int tc_pick_bn(int cn, long m_tiles);
+struct WgradPlan {
+    int bn, n_nblk, n_pairs, splits, ones_block;
+    long tokens_per_split;
+};
+WgradPlan tc_wgrad_plan(int64_t n, int cin, int cout, int kk);
+size_t tc_wgrad_plan_ws_bytes(int64_t n, int cin, int cout, int kk);
+// fixed-order reduction of per-split fp32 partials into the 16-bit gradient tensors
+int tc_wgrad_reduce_launch(const float* ws_w, int splits, const float* ws_b, int splits_b, void* gw, void* gb,
+                           long n_w, int cout, int fp16, cudaStream_t s);
 
 }  // namespace svtad
