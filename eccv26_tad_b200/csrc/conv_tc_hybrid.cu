@@ -46,7 +46,7 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                    const int32_t* __restrict__ nbr, const uint16_t* __restrict__ bias,
                    uint16_t* __restrict__ out, const int32_t* __restrict__ status, long n, int cred, int cn,
                    int kk, int tpb, int nstage, int fp16, int m_tiles, int n_blks, int rotate,
-                   int* __restrict__ err, int dbg) {
+                   int* __restrict__ err) {
     if (DGRAD && status != nullptr && (__ldg(status) & SVTAD_TABLE_ASYMMETRIC)) return;
     constexpr int B_TILE_BYTES = b_tile_bytes_for(BN);
     constexpr int B_TX_BYTES = DGRAD ? BN * 128 : B_TILE_BYTES;
@@ -130,23 +130,22 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
             // every tile walks the (tap, channel chunk) steps from its own starting point, so that CTAs
             // running side by side pull different weight tiles out of L2 instead of the same one
             const int rot = rotate ? (int)(((long)tile * 11) % stages_per_tile) : 0;
-            for (int st = 0; st < stages_per_tile; ++st) {
+            // first step of this tile that this warp owns; then every A_WARPS-th one.  Slot, phase and
+            // (tap, chunk) advance incrementally: no division in the loop.
+            int st = (warp - it0) & (A_WARPS - 1);
+            int s = (it0 + st) % nstage;
+            uint32_t ph = (((it0 + st) / nstage) & 1) ^ 1;
+            int sr = (st + rot) % stages_per_tile;
+            int k = sr / kchunks, kc = sr - k * kchunks;
+            for (; st < stages_per_tile; st += A_WARPS) {
                 const int it = it0 + st;
-                if ((it & (A_WARPS - 1)) != warp) continue;
-                int sr = st + rot;
-                if (sr >= stages_per_tile) sr -= stages_per_tile;
-                const int k = sr / kchunks, kc = sr - k * kchunks;
-                const int s = it % nstage;
-                if (!warp_wait(smem_u32(&tail->empty[s]), ((it / nstage) & 1) ^ 1, s_abort, err, 41, lane)) { alive = false; break; }
+                if (!warp_wait(smem_u32(&tail->empty[s]), ph, s_abort, err, 41, lane)) { alive = false; break; }
                 const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
                 const uint32_t bar = smem_u32(&tail->full[s]);
                 const int c0 = kc * STAGE_K;
                 if (lane == 0) {
                     const uint32_t b_tile = a_tile + A_TILE_BYTES;
                     const int wtap = DGRAD ? (kk - 1 - k) : k;
-                    if (dbg & 4) {
-                        mbar_arrive(bar);            // timing experiment: no weight tile
-                    } else {
                     mbar_expect_tx(bar, B_TX_BYTES);
                     if (!DGRAD) {
 #pragma unroll
@@ -155,19 +154,26 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                     } else {
                         tma_load_3d(b_tile, &map_w, c0, n0, wtap, bar);
                     }
-                    }
                 }
                 // A: 128 rows x 8 chunks of 16 B; 8 consecutive lanes cover one row's 128 B
                 const uint16_t* abase = a + c0 + sub * 8;
                 const int* trow = tab + rg * kk + k;
-#pragma unroll 8
-                for (int itr = 0; itr < ((dbg & 1) ? 0 : 32); ++itr) {
-                    const int j = trow[itr * 4 * kk];
+                // all row numbers first, then the copies back to back
+                int jrow[32];
+#pragma unroll
+                for (int itr = 0; itr < 32; ++itr) jrow[itr] = trow[itr * 4 * kk];
+#pragma unroll
+                for (int itr = 0; itr < 32; ++itr) {
+                    const int j = jrow[itr];
                     const int r7 = ((itr & 1) << 2) | rg;            // (row & 7) for row = itr * 4 + rg
                     const uint32_t dst = a_tile + (itr * 4 + rg) * 128 + ((sub ^ r7) << 4);
                     cp_async16(dst, abase + (long)(j < 0 ? 0 : j) * cred, j < 0 ? 0u : 16u);
                 }
                 cp_async_arrive_noinc(bar);
+                s += A_WARPS;
+                while (s >= nstage) { s -= nstage; ph ^= 1u; }
+                kc += A_WARPS;
+                while (kc >= kchunks) { kc -= kchunks; if (++k == kk) k = 0; }
             }
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
@@ -176,17 +182,17 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
         if (lane == 0) {
             const uint32_t idesc = make_idesc(fp16 ? 0 : 1, 0, DGRAD ? 0 : 1, TILE_M, BN);
             bool alive = true;
-            int it = 0, local = 0;
+            int it = 0, local = 0, s = 0;
+            uint32_t ph = 0;
             for (int tile = blockIdx.x; tile < tiles_total && alive; tile += gridDim.x, ++local) {
                 const int buf = local & 1;
                 if (!mbar_wait(smem_u32(&tail->accum_empty[buf]), ((local >> 1) & 1) ^ 1, s_abort, err, 42)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int st = 0; st < stages_per_tile; ++st, ++it) {
-                    const int s = it % nstage;
-                    if (!mbar_wait(smem_u32(&tail->full[s]), (it / nstage) & 1, s_abort, err, 43)) { alive = false; break; }
-                    if (!(dbg & 8)) fence_proxy_async();   // cp.async (generic proxy) writes -> tcgen05.mma (async proxy) reads
-                    if (!(dbg & 16)) tc_fence_after();
+                    if (!mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 43)) { alive = false; break; }
+                    fence_proxy_async();   // cp.async (generic proxy) writes -> tcgen05.mma (async proxy) reads
+                    tc_fence_after();
                     const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
                     const uint32_t b_tile = a_tile + A_TILE_BYTES;
 #pragma unroll
@@ -194,9 +200,10 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                         uint64_t ad = make_smem_desc(a_tile + ks * 32, 0, 1024);
                         uint64_t bd = DGRAD ? make_smem_desc(b_tile + ks * 32, 0, 1024)
                                             : make_smem_desc(b_tile + ks * 2048, 8192, 1024);
-                        if (!(dbg & 2)) umma_f16(d_tmem, ad, bd, idesc, (st | ks) != 0 ? 1u : 0u);
+                        umma_f16(d_tmem, ad, bd, idesc, (st | ks) != 0 ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&tail->empty[s]));
+                    if (++s == nstage) { s = 0; ph ^= 1u; }
                 }
                 if (alive) umma_commit(smem_u32(&tail->accum_full[buf]));
             }
@@ -344,13 +351,14 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
         int nxt[4] = {-1, -1, -1, -1};
         if (warp < total_stages) fetch(src_stage(warp), nxt);
         int local = 0;
+        int s = warp % nstage;
+        uint32_t ph = ((warp / nstage) & 1) ^ 1;
         for (int it = warp; it < total_stages; it += A_WARPS, ++local) {
             int* idx = my_idx + (local & 1) * TILE_M;
             *reinterpret_cast<int4*>(idx + lane * 4) = make_int4(nxt[0], nxt[1], nxt[2], nxt[3]);
             __syncwarp();
             if (it + A_WARPS < total_stages) fetch(src_stage(it + A_WARPS), nxt);
-            const int s = it % nstage;
-            if (!warp_wait(smem_u32(&tail->empty[s]), ((it / nstage) & 1) ^ 1, s_abort, err, 51, lane)) break;
+            if (!warp_wait(smem_u32(&tail->empty[s]), ph, s_abort, err, 51, lane)) break;
             const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
             const uint32_t bar = smem_u32(&tail->full[s]);
             if (lane == 0) {
@@ -372,15 +380,18 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
                 cp_async16(dst, src, j < 0 ? 0u : 16u);
             }
             cp_async_arrive_noinc(bar);
+            s += A_WARPS;
+            while (s >= nstage) { s -= nstage; ph ^= 1u; }
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
     } else if (warp == 4) {
         if (lane == 0) {
             const uint32_t idesc = make_idesc(fp16 ? 0 : 1, 1, 1, TILE_M, BN);
             bool alive = true;
+            int s = 0;
+            uint32_t ph = 0;
             for (int it = 0; it < total_stages; ++it) {
-                const int s = it % nstage;
-                if (!mbar_wait(smem_u32(&tail->full[s]), (it / nstage) & 1, s_abort, err, 52)) { alive = false; break; }
+                if (!mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 52)) { alive = false; break; }
                 fence_proxy_async();
                 tc_fence_after();
                 const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
@@ -392,6 +403,7 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
                     umma_f16(tmem_base, ad, bd, idesc, (it | ks) != 0 ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&tail->empty[s]));
+                if (++s == nstage) { s = 0; ph ^= 1u; }
             }
             if (alive && total_stages > 0) umma_commit(smem_u32(&tail->accum_full[0]));
         }
@@ -456,8 +468,6 @@ static int launch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaStre
     const size_t extra = sizeof(TmaTail) + 2 * (size_t)TILE_M * p.kk * sizeof(int);
     int nstage = (int)((TC_SMEM_LIMIT - 1024 - extra) / stage);
     if (nstage > 8) nstage = 8;
-    if (getenv("SVTAD_TC_NSTAGE") && atoi(getenv("SVTAD_TC_NSTAGE")) >= 2 && atoi(getenv("SVTAD_TC_NSTAGE")) < nstage)
-        nstage = atoi(getenv("SVTAD_TC_NSTAGE"));
     if (nstage < 2)
         return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core conv: not enough shared memory for BN=%d kk=%d", BN, p.kk);
     const size_t smem = 1024 + nstage * stage + extra;
@@ -469,8 +479,7 @@ static int launch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaStre
     int grid = (int)(tiles < tc_num_sms() ? tiles : tc_num_sms());
     kern<<<grid, HY_THREADS, smem, s>>>(map_w, (const uint16_t*)p.a, p.nbr, (const uint16_t*)p.bias,
                                         (uint16_t*)p.out, status, (long)p.n, cred, cn, p.kk, p.tpb, nstage, fp16,
-                                        m_tiles, n_blks, tc_rotate_enabled() ? 1 : 0, tc_error_ptr(),
-                                        getenv("SVTAD_TC_DEBUG") ? atoi(getenv("SVTAD_TC_DEBUG")) : 0);
+                                        m_tiles, n_blks, tc_rotate_enabled() ? 1 : 0, tc_error_ptr());
     SV_LAUNCH_CHECK("conv_hybrid_kernel");
     return SVTAD_OK;
 }
