@@ -77,10 +77,12 @@ int tc_make_map(CUtensorMap* map, int rank, const void* base, const uint64_t* di
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return set_error(SVTAD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     // the driver call needs this thread to hold the device's context (autograd worker threads may not yet)
-    static thread_local bool ctx_ready = false;
-    if (!ctx_ready) {
-        SV_CUDA(cudaFree(nullptr));
-        ctx_ready = true;
+    static thread_local int ctx_dev = -1;
+    int dev = 0;
+    SV_CUDA(cudaGetDevice(&dev));
+    if (ctx_dev != dev) {
+        SV_CUDA(cudaSetDevice(dev));   // binds the device's primary context to this thread; allocates nothing
+        ctx_dev = dev;
     }
     cuuint64_t gdim[3], gstride[2];
     cuuint32_t bx[3], es[3] = {1, 1, 1};
