@@ -29,6 +29,8 @@ SIGNATURES = {
     "svtad_conv_fwd": (c_int, [c_p, c_p, c_p, c_p, c_p, c_i64, c_int, c_int, c_int, c_int, c_int, c_p, c_sz, c_p]),
     "svtad_conv_dgrad": (c_int, [c_p, c_p, c_p, c_p, c_i64, c_int, c_int, c_int, c_int, c_int, c_p, c_p, c_sz, c_p]),
     "svtad_conv_wgrad": (c_int, [c_p, c_p, c_p, c_p, c_p, c_i64, c_int, c_int, c_int, c_int, c_int, c_p, c_sz, c_p]),
+    "svtad_static_workspace_bytes": (c_sz, []),
+    "svtad_conv_wgrad_static": (c_int, [c_p, c_p, c_p, c_p, c_p, c_i64, c_int, c_int, c_int, c_int, c_int, c_p]),
     "svtad_device_error": (c_int, [ctypes.POINTER(ctypes.c_int32)]),
     "svtad_path_for": (c_int, [c_int, c_i64, c_int, c_int, c_int, c_int]),
 }

@@ -175,6 +175,29 @@ def conv_wgrad(gy, x, nbr, kk, tokens_per_batch=0, with_bias=True):
     return gw, gb
 
 
+def conv_wgrad_static(gy, x, nbr, gw, gb, tokens_per_batch=0):
+    """Weight / bias gradient into caller-provided ``gw`` / ``gb`` with the library's built-in workspace.
+
+    For callers that must not allocate on the device once they are running (device memory owned by the
+    host's own arena, allocation forbidden after start-up): nothing is allocated here, neither by the
+    library nor by torch.  ``gb`` may be None.  Problems whose
+    workspace exceeds the built-in array raise; calls that overlap on the GPU share the array and race.
+    """
+    _require_cuda(gy, x, nbr, gw, gb)
+    code = _dtype_code(x)
+    kk, cin, cout = gw.shape
+    for t in (gy, x, nbr, gw) + ((gb,) if gb is not None else ()):
+        if not t.is_contiguous():
+            raise ValueError("conv_wgrad_static needs contiguous tensors (it cannot make copies)")
+    if nbr.dtype != torch.int32 or gy.dtype != x.dtype or gw.dtype != x.dtype:
+        raise ValueError("conv_wgrad_static: nbr must be int32 and gy, x, gw must share one dtype")
+    n = x.numel() // cin
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.load().svtad_conv_wgrad_static(_ptr(gy), _ptr(x), _ptr(nbr), _ptr(gw), _ptr(gb), n, cin,
+                                                       cout, kk, tokens_per_batch, code, _stream()))
+    return gw, gb
+
+
 def device_error():
     """Reads and clears the device error word (synchronises).  0 = no bounded wait gave up."""
     import ctypes

@@ -136,6 +136,29 @@ int svtad_conv_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw
                      void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * svtad_conv_wgrad for callers that cannot allocate device memory (no counterpart in the reference).
+ * Who needs it: hosts that must not call cudaMalloc once they are running - servers that gave all
+ * device memory to their own arena, plugins whose host forbids allocation after start-up, loops that
+ * cannot afford the implicit synchronisation of an allocation.  The per-split partial sums go to an array
+ * of SVTAD_STATIC_WS_BYTES that is part of the library's device image, so every GPU that loads the
+ * library holds that much memory until the process exits.  The call itself allocates nothing
+ * (no cudaMalloc / cudaFree, no allocating library routine).
+ *   - Limit: problems with svtad_workspace_bytes(SVTAD_OP_WGRAD, ...) > SVTAD_STATIC_WS_BYTES are
+ *     refused with SVTAD_ERR_WORKSPACE (C = 192 and 256 at 3x3 fit; C = 1024 does not).
+ *   - The first call on a device looks the array's address up (cudaGetSymbolAddress, with that
+ *     device current); make that first call before any stream capture.
+ *   - All calls on a device share the array and it keeps the previous call's contents.  Nothing in
+ *     it needs clearing between calls, but two calls that overlap on the GPU (different streams)
+ *     race on it: keep them on one stream or order them with events.
+ * Arguments and results as svtad_conv_wgrad, minus the workspace.
+ */
+#define SVTAD_STATIC_WS_BYTES (32u << 20)
+size_t svtad_static_workspace_bytes(void);
+int svtad_conv_wgrad_static(const void* gy, const void* x, const int32_t* nbr, void* gw, void* gb,
+                            int64_t n, int cin, int cout, int kk, int tokens_per_batch, int dtype,
+                            void* stream);
+
+/*
  * Reads (and clears) the device-side error word of the current device: non-zero means a bounded
  * wait inside a tensor-core kernel gave up and that launch's output is invalid.  Synchronises
  * the device.  No reference counterpart.
