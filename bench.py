@@ -246,6 +246,7 @@ def main():
     import torch
     import torch.distributed as dist
     from eccv26_tad_b200 import SparseConv2d, build_neighbor_table, ops
+    from eccv26_tad_b200.distributed import allreduce_weight_grads
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -294,9 +295,10 @@ def main():
             ops._lib.check(lib.svtad_conv_wgrad(it["gy"].data_ptr(), it["x"].data_ptr(), it["table"].data_ptr(),
                                                 gw_buf.data_ptr(), gb_buf.data_ptr(), n, C, C, KK, 0, code,
                                                 ws.data_ptr(), ws_bytes, stream))
-            nl += 5   # fwd, dgrad, wgrad partial, bias partial, finalize
+            nl += 5   # fwd, dgrad, wgrad partials, (bias partial), reduce
+            nl -= 1   # bias gradient comes out of the wgrad kernel (all-ones block), no separate launch
             if world > 1:
-                dist.all_reduce(grads)
+                allreduce_weight_grads(gw_buf, gb_buf, bucket=grads)
         return nl
 
     stream = torch.cuda.Stream(device=dev)
@@ -356,38 +358,46 @@ def main():
 
     # ---------------------------------------------------------------- per-kernel durations (instrumented repeat)
     def time_op(fn, reps):
-        # `reps` launches back to back between two events, each on a different resident input set
+        """Average device time of one launch: `reps` launches on rotating input sets captured into one CUDA
+        graph (no host launch overhead between them), replayed between two events."""
         with torch.cuda.stream(stream):
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            try:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    for i in range(reps):
+                        fn(i, torch.cuda.current_stream().cuda_stream)
+                run = g.replay
+            except Exception:
+                torch.cuda.synchronize()
+                run = lambda: [fn(i, stream.cuda_stream) for i in range(reps)]
+            run()
             stream.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record(stream)
-            for i in range(reps):
-                fn(i)
+            run()
             b.record(stream)
             b.synchronize()
             return a.elapsed_time(b) / reps
 
-    sc = stream.cuda_stream
     per_kernel = {}
     reps = 24
     for ki, r in enumerate(KEEPS):
-        def f_fwd(i, ki=ki):
+        def f_fwd(i, sc, ki=ki):
             it = dsets[i % N_SETS][ki]
             lib.svtad_conv_fwd(it["x"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(), bias.data_ptr(),
                                y_buf.data_ptr(), it["n"], C, C, KK, 0, code, None, 0, sc)
 
-        def f_dg(i, ki=ki):
+        def f_dg(i, sc, ki=ki):
             it = dsets[i % N_SETS][ki]
             lib.svtad_conv_dgrad(it["gy"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(), gx_buf.data_ptr(),
                                  it["n"], C, C, KK, 0, code, None, None, 0, sc)
 
-        def f_wg(i, ki=ki):
+        def f_wg(i, sc, ki=ki):
             it = dsets[i % N_SETS][ki]
             lib.svtad_conv_wgrad(it["gy"].data_ptr(), it["x"].data_ptr(), it["table"].data_ptr(), gw_buf.data_ptr(),
                                  gb_buf.data_ptr(), it["n"], C, C, KK, 0, code, ws.data_ptr(), ws_bytes, sc)
 
         for name, fn in (("fwd", f_fwd), ("dgrad", f_dg), ("wgrad", f_wg)):
-            time_op(fn, 3)
             per_kernel[(name, ki)] = time_op(fn, reps)
     torch.cuda.synchronize()
     totals = {name: sum(per_kernel[(name, ki)] for ki in range(len(KEEPS))) for name in ("fwd", "dgrad", "wgrad")}
@@ -396,8 +406,8 @@ def main():
     dom_flops = sum(flops_pass(host_sets[0][ki]["n"]) for ki in range(len(KEEPS)))
     achieved = dom_flops / (totals[dominant] * 1e-3) / 1e12
     roofline = {
-        "bound": "tensor", "kernel": {"fwd": "conv_tc_kernel<BN,false>", "dgrad": "conv_tc_kernel<BN,true>",
-                                      "wgrad": "wgrad_tc_kernel<BN> (+ bias partial + finalize)"}[dominant],
+        "bound": "tensor", "kernel": {"fwd": "conv_hybrid_kernel<BN,false>", "dgrad": "conv_hybrid_kernel<BN,true>",
+                                      "wgrad": "wgrad_hybrid_kernel<BN> + wgrad_reduce4_kernel"}[dominant],
         "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
         "peak_source": f"{peak_kind} bf16 burst", "traffic": NCU_TRAFFIC_BYTES.get(dominant),
         "flops_per_launch": {f"keep{int(r * 100)}": flops_pass(host_sets[0][ki]["n"]) for ki, r in enumerate(KEEPS)},
@@ -434,8 +444,8 @@ def main():
                 y = module(x, table)
             y.backward(gy)
             if world > 1:
-                dist.all_reduce(module.weight.grad)
-                dist.all_reduce(module.bias.grad)
+                gw_r, gb_r = allreduce_weight_grads(module.weight.grad, module.bias.grad)
+                module.weight.grad, module.bias.grad = gw_r, gb_r
             out_h[ki]["y"].copy_(y, non_blocking=True)
             out_h[ki]["gx"].copy_(x.grad, non_blocking=True)
             gw_h.copy_(module.weight.grad, non_blocking=True)

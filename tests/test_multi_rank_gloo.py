@@ -1,0 +1,78 @@
+"""CPU tier: the N > 1 path on two gloo ranks.  Clips are independent, so summing the per-rank weight
+gradients (one flat all-reduce) must equal the single-rank gradient of the whole batch; forward and
+input-gradient rows of a rank's clips must equal the same rows of the whole-batch result."""
+import os
+import socket
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from eccv26_tad_b200.distributed import allreduce_weight_grads, shard_clips
+from oracle import conv as oconv
+from oracle import table as otab
+
+CLIPS, T, H, W, C, K_KEEP = 5, 2, 6, 6, 8, 11
+
+
+def _problem():
+    rng = np.random.default_rng(17)
+    scores = rng.standard_normal((CLIPS * T, H * W)).astype(np.float32)
+    kept, table = otab.build_table(scores, K_KEEP, H, W, 3)
+    n = table.shape[0]
+    x = rng.standard_normal((n, C)).astype(np.float32)
+    gy = rng.standard_normal((n, C)).astype(np.float32)
+    w = rng.standard_normal((9, C, C)).astype(np.float32)
+    return table, x, gy, w
+
+
+def _worker(rank, world, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        table, x, gy, w = _problem()
+        rows_per_clip = T * K_KEEP
+        clips = shard_clips(CLIPS, rank, world)
+        lo, hi = clips.start * rows_per_clip, clips.stop * rows_per_clip
+        # a rank's table is rank-local: renumber its rows from zero
+        tab = table[lo:hi].copy()
+        tab[tab >= 0] -= lo
+        y = oconv.fwd(x[lo:hi], tab, w, None)
+        gx = oconv.dgrad(gy[lo:hi], tab, w)
+        gw, gb = oconv.wgrad(gy[lo:hi], x[lo:hi], tab, 9)
+        gw_t, gb_t = allreduce_weight_grads(torch.from_numpy(gw), torch.from_numpy(gb))
+        out[rank] = dict(lo=lo, hi=hi, y=y, gx=gx, gw=gw_t.numpy().copy(), gb=gb_t.numpy().copy())
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_match_single_rank():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_worker, args=(2, port, out), nprocs=2, join=True)
+        out = dict(out)
+    table, x, gy, w = _problem()
+    y = oconv.fwd(x, table, w, None)
+    gx = oconv.dgrad(gy, table, w)
+    gw, gb = oconv.wgrad(gy, x, table, 9)
+    covered = 0
+    for r in (0, 1):
+        o = out[r]
+        np.testing.assert_allclose(o["y"], y[o["lo"]:o["hi"]], rtol=0, atol=1e-12)
+        np.testing.assert_allclose(o["gx"], gx[o["lo"]:o["hi"]], rtol=0, atol=1e-12)
+        np.testing.assert_allclose(o["gw"], gw, rtol=1e-12, atol=1e-12)
+        np.testing.assert_allclose(o["gb"], gb, rtol=1e-12, atol=1e-12)
+        covered += o["hi"] - o["lo"]
+    assert covered == table.shape[0]
+
+
+def test_shard_clips_partitions():
+    for n, world in [(8, 1), (8, 2), (8, 8), (5, 2), (3, 4)]:
+        seen = []
+        for r in range(world):
+            seen += list(shard_clips(n, r, world))
+        assert seen == list(range(n))
