@@ -49,9 +49,9 @@ N_SETS = 8
 FALLBACK_TFLOPS = 1590.0
 FALLBACK_HBM = 6650.0
 METRIC = "SparseConv2D retained tokens/sec fwd+bwd at keep 10-55%"
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu capture
-# summarised under profiles/ (None until a capture exists for the kernel that dominates)
-NCU_TRAFFIC_BYTES = {}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised under profiles/
+# (226 560-row case, C=192), divided by the rows of that launch; traffic grows in proportion to the rows
+NCU_DRAM_BYTES_PER_ROW = {"fwd": 138.04e6 / 226560, "dgrad": 137.44e6 / 226560, "wgrad": 235.20e6 / 226560}
 
 
 def flops_pass(n):
@@ -409,7 +409,8 @@ def main():
         "bound": "tensor", "kernel": {"fwd": "conv_hybrid_kernel<BN,false>", "dgrad": "conv_hybrid_kernel<BN,true>",
                                       "wgrad": "wgrad_hybrid_kernel<BN> + wgrad_reduce4_kernel"}[dominant],
         "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
-        "peak_source": f"{peak_kind} bf16 burst", "traffic": NCU_TRAFFIC_BYTES.get(dominant),
+        "peak_source": f"{peak_kind} bf16 burst", "traffic": NCU_DRAM_BYTES_PER_ROW[dominant] * tokens_step / len(KEEPS),
+        "traffic_note": "ncu DRAM bytes per row of the 226560-row capture x mean rows per launch",
         "flops_per_launch": {f"keep{int(r * 100)}": flops_pass(host_sets[0][ki]["n"]) for ki, r in enumerate(KEEPS)},
         "ms_per_launch": {f"{name}_keep{int(KEEPS[ki] * 100)}": v for (name, ki), v in per_kernel.items()},
         "all_kernels_frac": {name: dom_flops / (totals[name] * 1e-3) / 1e12 / peak_tf for name in totals},
