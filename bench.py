@@ -283,20 +283,27 @@ def main():
     gw_buf, gb_buf = grads[:KK * C * C], grads[KK * C * C:]
     launches_per_step = 0
 
-    def raw_step(dk, stream, count=False):
-        """One step through the C ABI on resident buffers: 3 keep rates x (fwd, dgrad, wgrad+bias)."""
+    side = torch.cuda.Stream(device=dev)
+
+    def raw_step(dk, stream=None, count=False):
+        """One step through the C ABI on resident buffers: 3 keep rates x (fwd, then dgrad and wgrad+bias).
+        The two halves of the backward are independent, so wgrad runs on a side stream next to dgrad."""
         nl = 0
+        cur = torch.cuda.current_stream()
         for it in dk:
             n = it["n"]
             ops._lib.check(lib.svtad_conv_fwd(it["x"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(),
-                                              bias.data_ptr(), y_buf.data_ptr(), n, C, C, KK, 0, code, None, 0, stream))
-            ops._lib.check(lib.svtad_conv_dgrad(it["gy"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(),
-                                                gx_buf.data_ptr(), n, C, C, KK, 0, code, None, None, 0, stream))
+                                              bias.data_ptr(), y_buf.data_ptr(), n, C, C, KK, 0, code, None, 0,
+                                              cur.cuda_stream))
+            side.wait_stream(cur)
             ops._lib.check(lib.svtad_conv_wgrad(it["gy"].data_ptr(), it["x"].data_ptr(), it["table"].data_ptr(),
                                                 gw_buf.data_ptr(), gb_buf.data_ptr(), n, C, C, KK, 0, code,
-                                                ws.data_ptr(), ws_bytes, stream))
-            nl += 5   # fwd, dgrad, wgrad partials, (bias partial), reduce
-            nl -= 1   # bias gradient comes out of the wgrad kernel (all-ones block), no separate launch
+                                                ws.data_ptr(), ws_bytes, side.cuda_stream))
+            ops._lib.check(lib.svtad_conv_dgrad(it["gy"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(),
+                                                gx_buf.data_ptr(), n, C, C, KK, 0, code, None, None, 0,
+                                                cur.cuda_stream))
+            cur.wait_stream(side)
+            nl += 4   # fwd, dgrad, wgrad partials (bias row included), reduce
             if world > 1:
                 allreduce_weight_grads(gw_buf, gb_buf, bucket=grads)
         return nl
@@ -305,7 +312,7 @@ def main():
     graphs = None
     with torch.cuda.stream(stream):
         for s in range(min(3, N_SETS)):
-            launches_per_step = raw_step(dsets[s], stream.cuda_stream)
+            launches_per_step = raw_step(dsets[s])
         stream.synchronize()
         if not args.no_graph:
             try:
@@ -313,7 +320,7 @@ def main():
                 for s in range(N_SETS):
                     g = torch.cuda.CUDAGraph()
                     with torch.cuda.graph(g, stream=stream):
-                        raw_step(dsets[s], torch.cuda.current_stream().cuda_stream)
+                        raw_step(dsets[s])
                     graphs.append(g)
             except Exception as e:   # stay measurable without graphs
                 sys.stderr.write(f"[bench] CUDA graph capture failed ({e}); launching eagerly\n")
@@ -326,7 +333,7 @@ def main():
             if graphs is not None:
                 graphs[s].replay()
             else:
-                raw_step(dsets[s], torch.cuda.current_stream().cuda_stream)
+                raw_step(dsets[s])
 
     def barrier():
         if world > 1:

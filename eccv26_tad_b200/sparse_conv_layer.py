@@ -16,6 +16,7 @@ Differences, all additive:
   take the reference's scatter formulation, so results are defined for any table.
 """
 import math
+import os
 
 import torch
 import torch.nn as nn
@@ -53,6 +54,15 @@ class _PerTableCache:
 
 
 _table_cache = _PerTableCache()
+_OVERLAP_BACKWARD = os.environ.get("SVTAD_OVERLAP_BACKWARD", "1") != "0"
+_side_streams = {}
+
+
+def _side_stream(device):
+    key = torch.device(device).index
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=device)
+    return _side_streams[key]
 
 
 def _status_for(nbr, tokens_per_batch):
@@ -87,16 +97,36 @@ class SparseConv2dFunction(Function):
         tpb = ctx.tokens_per_batch
         nbr = neighbor_indices.reshape(-1, kk)
         grad_input = grad_weight = grad_bias = None
-        if ctx.needs_input_grad[0]:
+        need_b = bias is not None and ctx.needs_input_grad[3]
+        need_w = ctx.needs_input_grad[2] or need_b
+        need_x = ctx.needs_input_grad[0]
+        # the two halves of the backward are independent: the weight gradient runs on a side stream
+        # next to the input gradient (the reference launches them one after the other, :100-117)
+        side = _side_stream(grad_output.device) if (need_w and need_x and _OVERLAP_BACKWARD) else None
+        x2 = x.reshape(-1, ctx.C_in)
+        if need_w:
+            if side is not None:
+                cur = torch.cuda.current_stream(grad_output.device)
+                side.wait_stream(cur)
+                with torch.cuda.stream(side):
+                    gw, gb = ops.conv_wgrad(grad_output, x2, nbr, kk, tpb, with_bias=need_b)
+                for t in (grad_output, x2, nbr):
+                    t.record_stream(side)
+            else:
+                gw, gb = ops.conv_wgrad(grad_output, x2, nbr, kk, tpb, with_bias=need_b)
+        if need_x:
             status = ctx.table_status
             if status is None:
                 status = _status_for(neighbor_indices, tpb)
             grad_input = ops.conv_dgrad(grad_output, nbr, weight, tpb, table_status=status)
             if x.dim() == 3:
                 grad_input = grad_input.view(x.shape)
-        need_b = bias is not None and ctx.needs_input_grad[3]
-        if ctx.needs_input_grad[2] or need_b:
-            gw, gb = ops.conv_wgrad(grad_output, x.reshape(-1, ctx.C_in), nbr, kk, tpb, with_bias=need_b)
+        if need_w:
+            if side is not None:
+                cur.wait_stream(side)
+                gw.record_stream(cur)
+                if gb is not None:
+                    gb.record_stream(cur)
             if ctx.needs_input_grad[2]:
                 grad_weight = gw
             if need_b:
