@@ -27,6 +27,7 @@ def _ops():
 def _no_forced_path(monkeypatch):
     monkeypatch.delenv("SVTAD_FORCE_PATH", raising=False)
     monkeypatch.delenv("SVTAD_TC_BN", raising=False)
+    monkeypatch.delenv("SVTAD_TC_WGRAD_CLUSTER", raising=False)
     yield
     assert _ops().device_error() == 0, "a bounded wait inside a tensor-core kernel gave up"
 
@@ -95,6 +96,18 @@ def test_tc_column_block_variants(bn, monkeypatch):
     x, w, b, gy = make_conv_inputs(n, 192, 192, 3, torch.bfloat16, 99, bias="random")
     outs = _run_all(table, x, w, b, gy)
     _check_all(table, x, w, b, gy, outs, 2e-2)
+
+
+def test_wgrad_cluster_reduction_variant(monkeypatch):
+    """Optional wgrad form: the splits of a block pair reduce through distributed shared memory."""
+    monkeypatch.setenv("SVTAD_TC_WGRAD_CLUSTER", "1")
+    for B, T, keep in [(2, 80, 0.1), (1, 30, 0.55), (1, 1, 0.3)]:
+        _, _, table = make_table(B, T, 14, 14, keep, 3, 123)
+        n = table.shape[0]
+        x, w, b, gy = make_conv_inputs(n, 192, 192, 3, torch.bfloat16, 123, bias="random")
+        outs = _run_all(table, x, w, b, gy)
+        _check_all(table, x, w, b, gy, outs, 2e-2)
+    monkeypatch.setenv("SVTAD_TC_WGRAD_CLUSTER", "0")
 
 
 def test_tc_and_simt_agree_tightly(monkeypatch):
