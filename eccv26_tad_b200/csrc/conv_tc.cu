@@ -52,6 +52,13 @@ int tc_num_sms() {
     return cached;
 }
 
+bool tc_pdl_enabled() {
+    // off by default: back-to-back launches gain 0.3-0.5 us each, but a step that forks wgrad onto a side
+    // stream got slower with it on B200 (0.187 vs 0.178 ms)
+    const char* e = getenv("SVTAD_PDL");
+    return e != nullptr && e[0] == '1';
+}
+
 bool tc_rotate_enabled() {
     const char* e = getenv("SVTAD_TC_ROTATE");
     return !(e != nullptr && e[0] == '0');
@@ -177,6 +184,7 @@ size_t tc_wgrad_ws_bytes(int64_t n, int cin, int cout, int kk) { return tc_wgrad
 __global__ void __launch_bounds__(256)
 wgrad_reduce4_kernel(const float* __restrict__ ws_w, int splits, const float* __restrict__ ws_b, int splits_b,
                      uint16_t* __restrict__ gw, uint16_t* __restrict__ gb, long n_w, int cout, int fp16) {
+    pdl_wait();
     long e = (blockIdx.x * (long)blockDim.x + threadIdx.x) * 4;
     const float* src;
     uint16_t* dst;
@@ -204,9 +212,8 @@ wgrad_reduce4_kernel(const float* __restrict__ ws_w, int splits, const float* __
 int tc_wgrad_reduce_launch(const float* ws_w, int splits, const float* ws_b, int splits_b, void* gw, void* gb,
                            long n_w, int cout, int fp16, cudaStream_t s) {
     long total4 = (n_w + (gb ? cout : 0) + 3) / 4;
-    wgrad_reduce4_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, s>>>(
-        ws_w, splits, ws_b, splits_b, (uint16_t*)gw, (uint16_t*)gb, n_w, cout, fp16);
-    SV_LAUNCH_CHECK("wgrad_reduce4_kernel");
+    SV_CUDA(tc_launch(wgrad_reduce4_kernel, dim3((unsigned)((total4 + 255) / 256)), dim3(256), 0, s, ws_w, splits, ws_b,
+                      splits_b, (uint16_t*)gw, (uint16_t*)gb, n_w, cout, fp16));
     return SVTAD_OK;
 }
 

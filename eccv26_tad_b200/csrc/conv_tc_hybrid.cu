@@ -47,6 +47,8 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                    uint16_t* __restrict__ out, const int32_t* __restrict__ status, long n, int cred, int cn,
                    int kk, int tpb, int nstage, int fp16, int m_tiles, int n_blks, int rotate,
                    int* __restrict__ err) {
+    pdl_wait();                 // nothing of global memory is touched before the predecessor has finished
+    pdl_launch_dependents();    // the next kernel in the stream may begin its own launch now
     if (DGRAD && status != nullptr && (__ldg(status) & SVTAD_TABLE_ASYMMETRIC)) return;
     constexpr int B_TILE_BYTES = b_tile_bytes_for(BN);
     constexpr int B_TX_BYTES = DGRAD ? BN * 128 : B_TILE_BYTES;
@@ -266,6 +268,8 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
                     uint16_t* __restrict__ gw, uint16_t* __restrict__ gb,
                     long n, int cin, int cout, int kk, int tpb, long tokens_per_split, int n_nblk,
                     int nstage, int fp16, int ones_block, int rotate, int* __restrict__ err) {
+    pdl_wait();
+    pdl_launch_dependents();
     constexpr int B_TILE_BYTES = b_tile_bytes_for(BN);
     constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
     constexpr int TM_COLS = tmem_cols_for(BN);
@@ -530,10 +534,9 @@ static int launch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaStre
     const int n_blks = cn / BN;
     long tiles = (long)m_tiles * n_blks;
     int grid = (int)(tiles < tc_num_sms() ? tiles : tc_num_sms());
-    kern<<<grid, HY_THREADS, smem, s>>>(map_w, (const uint16_t*)p.a, p.nbr, (const uint16_t*)p.bias,
-                                        (uint16_t*)p.out, status, (long)p.n, cred, cn, p.kk, p.tpb, nstage, fp16,
-                                        m_tiles, n_blks, tc_rotate_enabled() ? 1 : 0, tc_error_ptr());
-    SV_LAUNCH_CHECK("conv_hybrid_kernel");
+    SV_CUDA(tc_launch(kern, dim3(grid), dim3(HY_THREADS), smem, s, map_w, (const uint16_t*)p.a, p.nbr,
+                      (const uint16_t*)p.bias, (uint16_t*)p.out, status, (long)p.n, cred, cn, p.kk, p.tpb, nstage, fp16,
+                      m_tiles, n_blks, tc_rotate_enabled() ? 1 : 0, tc_error_ptr()));
     return SVTAD_OK;
 }
 
@@ -595,10 +598,9 @@ static int launch_wgrad_hybrid(const void* gy, const void* x, const int32_t* nbr
     }
     auto kern = wgrad_hybrid_kernel<BN, false>;
     SV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, HY_THREADS, smem, s>>>(map_gy, (const uint16_t*)x, nbr, ws_w, ws_b, (uint16_t*)nullptr,
-                                        (uint16_t*)nullptr, (long)n, cin, cout, kk, tpb, pl.tokens_per_split,
-                                        pl.n_nblk, nstage, fp16, pl.ones_block, rot, tc_error_ptr());
-    SV_LAUNCH_CHECK("wgrad_hybrid_kernel");
+    SV_CUDA(tc_launch(kern, grid, dim3(HY_THREADS), smem, s, map_gy, (const uint16_t*)x, nbr, ws_w, ws_b,
+                      (uint16_t*)nullptr, (uint16_t*)nullptr, (long)n, cin, cout, kk, tpb, pl.tokens_per_split,
+                      pl.n_nblk, nstage, fp16, pl.ones_block, rot, tc_error_ptr()));
     return SVTAD_OK;
 }
 

@@ -197,7 +197,28 @@ struct alignas(16) TmaTail {   // 16-byte multiple: the table buffers behind it 
 constexpr int tmem_cols2_for(int bn) { return 2 * bn <= 64 ? 64 : 2 * bn <= 128 ? 128 : 2 * bn <= 256 ? 256 : 512; }
 
 
+// Programmatic dependent launch: a kernel launched with the attribute may start while its predecessor in
+// the stream is still draining; it must not touch global memory before pdl_wait().  Both are no-ops for
+// plain launches.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---- host helpers shared by the tensor-core translation units (defined in conv_tc.cu) ----
+bool tc_pdl_enabled();      // SVTAD_PDL=1 turns programmatic dependent launch on
+template <typename... KArgs, typename... Args>
+inline cudaError_t tc_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tc_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
 constexpr size_t TC_SMEM_LIMIT = 227 * 1024;
 int tc_num_sms();
 bool tc_rotate_enabled();   // SVTAD_TC_ROTATE=0 makes every CTA walk its K steps in the same order
