@@ -177,13 +177,13 @@ def cpu_port_run(steps, warmup, slices):
             oconv.dgrad(gy, table, wf, acc="f32")
             oconv.wgrad(gy, x, table, KK, acc="f32")
 
+    cores = oconv.set_threads(len(os.sched_getaffinity(0)))   # all host cores, whatever OMP_NUM_THREADS says
     for _ in range(warmup):
         step()
     t0 = time.perf_counter()
     for _ in range(steps):
         step()
     dt = time.perf_counter() - t0
-    cores = len(os.sched_getaffinity(0))
     return tokens * steps / dt, dt / steps * 1e3, cores, tokens
 
 
@@ -279,8 +279,13 @@ def main():
     n_max = max(it["n"] for it in host_sets[0])
     y_buf = torch.empty(n_max, C, dtype=torch.bfloat16, device=dev)
     gx_buf = torch.empty(n_max, C, dtype=torch.bfloat16, device=dev)
-    grads = torch.empty(KK * C * C + C, dtype=torch.bfloat16, device=dev)   # gw ++ gb, one all-reduce bucket
-    gw_buf, gb_buf = grads[:KK * C * C], grads[KK * C * C:]
+    # one flat bucket for the gradients of the step's three layers (gw ++ gb each), all-reduced once per step
+    # the way DDP buckets the adapters' gradients (reference: src/eccv26_tad.py:288-300, 25 MB buckets)
+    per_layer = KK * C * C + C
+    grads = torch.empty(len(KEEPS) * per_layer, dtype=torch.bfloat16, device=dev)
+    gw_bufs = [grads[i * per_layer:i * per_layer + KK * C * C] for i in range(len(KEEPS))]
+    gb_bufs = [grads[i * per_layer + KK * C * C:(i + 1) * per_layer] for i in range(len(KEEPS))]
+    gw_buf, gb_buf = gw_bufs[0], gb_bufs[0]
     launches_per_step = 0
 
     side = torch.cuda.Stream(device=dev)
@@ -290,22 +295,22 @@ def main():
         The two halves of the backward are independent, so wgrad runs on a side stream next to dgrad."""
         nl = 0
         cur = torch.cuda.current_stream()
-        for it in dk:
+        for li, it in enumerate(dk):
             n = it["n"]
             ops._lib.check(lib.svtad_conv_fwd(it["x"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(),
                                               bias.data_ptr(), y_buf.data_ptr(), n, C, C, KK, 0, code, None, 0,
                                               cur.cuda_stream))
             side.wait_stream(cur)
             ops._lib.check(lib.svtad_conv_wgrad(it["gy"].data_ptr(), it["x"].data_ptr(), it["table"].data_ptr(),
-                                                gw_buf.data_ptr(), gb_buf.data_ptr(), n, C, C, KK, 0, code,
+                                                gw_bufs[li].data_ptr(), gb_bufs[li].data_ptr(), n, C, C, KK, 0, code,
                                                 ws.data_ptr(), ws_bytes, side.cuda_stream))
             ops._lib.check(lib.svtad_conv_dgrad(it["gy"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(),
                                                 gx_buf.data_ptr(), n, C, C, KK, 0, code, None, None, 0,
                                                 cur.cuda_stream))
             cur.wait_stream(side)
             nl += 4   # fwd, dgrad, wgrad partials (bias row included), reduce
-            if world > 1:
-                allreduce_weight_grads(gw_buf, gb_buf, bucket=grads)
+        if world > 1:
+            dist.all_reduce(grads)
         return nl
 
     stream = torch.cuda.Stream(device=dev)
@@ -511,7 +516,12 @@ def main():
         }
         print(json.dumps(line))
     if world > 1:
-        dist.destroy_process_group()
+        # leave together, and without tearing the communicator down under live CUDA graphs
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def kernel_case(args):

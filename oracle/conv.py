@@ -32,6 +32,12 @@ def lib():
     return _lib
 
 
+def set_threads(n):
+    """Use n OpenMP threads in the timed (f32) functions; returns the count in effect."""
+    lib().svtad_oracle_set_threads(int(n))
+    return int(lib().svtad_oracle_get_threads())
+
+
 def _f32(a):
     return np.ascontiguousarray(np.asarray(a, dtype=np.float32))
 

@@ -162,4 +162,14 @@ static inline int64_t sv_off(int64_t i, int tpb) { return tpb > 0 ? (i / tpb) * 
 DEFINE_ORACLE(f32, float)
 DEFINE_ORACLE(f64, double)
 
-int svtad_oracle_version(void) { return 1; }
+int svtad_oracle_version(void) { return 2; }
+
+/* Number of OpenMP threads the timed functions use (launchers such as torchrun export OMP_NUM_THREADS=1). */
+#ifdef _OPENMP
+#include <omp.h>
+void svtad_oracle_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+int svtad_oracle_get_threads(void) { return omp_get_max_threads(); }
+#else
+void svtad_oracle_set_threads(int n) { (void)n; }
+int svtad_oracle_get_threads(void) { return 1; }
+#endif
