@@ -186,17 +186,22 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
             bool alive = true;
             int it = 0, local = 0, s = 0;
             uint32_t ph = 0;
+            bool ready = false;   // result of probing this step's barrier while the previous step's MMAs were issued
             for (int tile = blockIdx.x; tile < tiles_total && alive; tile += gridDim.x, ++local) {
                 const int buf = local & 1;
                 if (!mbar_wait(smem_u32(&tail->accum_empty[buf]), ((local >> 1) & 1) ^ 1, s_abort, err, 42)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int st = 0; st < stages_per_tile; ++st, ++it) {
-                    if (!mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 43)) { alive = false; break; }
+                    if (!ready && !mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 43)) { alive = false; break; }
                     fence_proxy_async();   // cp.async (generic proxy) writes -> tcgen05.mma (async proxy) reads
                     tc_fence_after();
                     const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
                     const uint32_t b_tile = a_tile + A_TILE_BYTES;
+                    int sn = s + 1;
+                    uint32_t phn = ph;
+                    if (sn == nstage) { sn = 0; phn ^= 1u; }
+                    ready = mbar_test_wait(smem_u32(&tail->full[sn]), phn);   // answer arrives while the MMAs issue
 #pragma unroll
                     for (int ks = 0; ks < STAGE_K / 16; ++ks) {
                         uint64_t ad = make_smem_desc(a_tile + ks * 32, 0, 1024);
@@ -205,7 +210,8 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                         umma_f16(d_tmem, ad, bd, idesc, (st | ks) != 0 ? 1u : 0u);
                     }
                     umma_commit(smem_u32(&tail->empty[s]));
-                    if (++s == nstage) { s = 0; ph ^= 1u; }
+                    s = sn;
+                    ph = phn;
                 }
                 if (alive) umma_commit(smem_u32(&tail->accum_full[buf]));
             }
@@ -397,12 +403,17 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
             bool alive = true;
             int s = 0;
             uint32_t ph = 0;
+            bool ready = false;
             for (int it = 0; it < total_stages; ++it) {
-                if (!mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 52)) { alive = false; break; }
+                if (!ready && !mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 52)) { alive = false; break; }
                 fence_proxy_async();
                 tc_fence_after();
                 const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
                 const uint32_t b_tile = a_tile + A_TILE_BYTES;
+                int sn = s + 1;
+                uint32_t phn = ph;
+                if (sn == nstage) { sn = 0; phn ^= 1u; }
+                ready = mbar_test_wait(smem_u32(&tail->full[sn]), phn);
 #pragma unroll
                 for (int ks = 0; ks < STAGE_K / 16; ++ks) {
                     uint64_t ad = make_smem_desc(a_tile + ks * 2048, 8192, 1024);
@@ -410,7 +421,8 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
                     umma_f16(tmem_base, ad, bd, idesc, (it | ks) != 0 ? 1u : 0u);
                 }
                 umma_commit(smem_u32(&tail->empty[s]));
-                if (++s == nstage) { s = 0; ph ^= 1u; }
+                s = sn;
+                ph = phn;
             }
             if (alive && total_stages > 0) umma_commit(smem_u32(&tail->accum_full[0]));
         }
