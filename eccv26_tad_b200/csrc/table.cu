@@ -60,15 +60,21 @@ __device__ __forceinline__ void tap_to_dydx(int tap, int ksize, int& dy, int& dx
     }
 }
 
+// floor(e / d) for e < 65536 with the host-computed multiplier ceil(2^32 / d)
+__device__ __forceinline__ int div_magic(int e, uint32_t magic) { return (int)__umulhi((uint32_t)e, magic); }
+
 template <int ITEMS, int KS>
 __global__ void __launch_bounds__(256)
 table_build_warp_kernel(const float* __restrict__ scores, int n_seg, int L, int k, int h, int w,
-                        int ksize, int32_t* __restrict__ kept_idx, int32_t* __restrict__ table,
-                        int64_t* __restrict__ idx64) {
+                        int ksize, uint32_t magic_w, uint32_t magic_hw, int32_t* __restrict__ kept_idx,
+                        int32_t* __restrict__ table, int64_t* __restrict__ idx64) {
     constexpr int WARPS = 8;
     constexpr int CAP = ITEMS * 32;
+    constexpr int KKMAX = (KS > 0) ? KS * KS : 49;
     __shared__ int16_t s_rank[WARPS][CAP];
     __shared__ uint32_t s_pos[WARPS][CAP];
+    constexpr int RR = (KS > 0 && KS <= 5) ? 32 : 8;   // kept tokens whose rows are staged per round
+    __shared__ int32_t s_out[WARPS][RR * KKMAX];     // staged table rows, written out with coalesced stores
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int seg = blockIdx.x * WARPS + wid;
     if (seg >= n_seg) return;
@@ -81,16 +87,23 @@ table_build_warp_kernel(const float* __restrict__ scores, int n_seg, int L, int 
         int e = j * 32 + lane;
         key[j] = (e < L) ? score_key(__ldg(sc + e)) : 0u;   // 0 is below every real key
     }
-    // k-th largest key: greatest T with count(key >= T) >= k, found bit by bit
+    // Threshold search, bit by bit from the top: T grows while count(key >= T) >= k.  As soon as the count
+    // is exactly k the kept set {key >= T} is decided and the remaining bits are skipped; if it never is
+    // (ties at the boundary) all 32 bits are walked and T ends as the k-th largest key.
     uint32_t T = 0;
+    if (L != k) {
 #pragma unroll 1
-    for (int bit = 31; bit >= 0; --bit) {
-        uint32_t cand = T | (1u << bit);
-        int c = 0;
+        for (int bit = 31; bit >= 0; --bit) {
+            uint32_t cand = T | (1u << bit);
+            int c = 0;
 #pragma unroll
-        for (int j = 0; j < ITEMS; ++j) c += (key[j] >= cand);
-        c = __reduce_add_sync(0xffffffffu, c);
-        if (c >= k) T = cand;
+            for (int j = 0; j < ITEMS; ++j) c += (key[j] >= cand);
+            c = __reduce_add_sync(0xffffffffu, c);
+            if (c >= k) {
+                T = cand;
+                if (c == k) break;
+            }
+        }
     }
     int gt = 0;
 #pragma unroll
@@ -113,8 +126,8 @@ table_build_warp_kernel(const float* __restrict__ scores, int n_seg, int L, int 
         int rank = run_keep + __popc(km & lt);
         if (valid) s_rank[wid][e] = keep ? (int16_t)rank : (int16_t)-1;
         if (keep) {
-            int p = e % hw;
-            int y = p / w, x = p - y * w;
+            int p = (hw == 1) ? 0 : e - div_magic(e, magic_hw) * hw;
+            int y = (w == 1) ? p : div_magic(p, magic_w), x = p - y * w;
             s_pos[wid][rank] = (uint32_t)e | ((uint32_t)y << 16) | ((uint32_t)x << 24);
         }
         run_tie += __popc(eqm);
@@ -129,23 +142,54 @@ table_build_warp_kernel(const float* __restrict__ scores, int n_seg, int L, int 
         for (int r = lane; r < k; r += 32) idx64[base + r] = (int64_t)(s_pos[wid][r] & 0xFFFFu);
     if (table == nullptr) return;
 
+    // one lane per kept token computes its K*K entries into shared memory; the warp then writes the
+    // staged rows (contiguous in the table) with 16-byte stores
     const int KK = (KS > 0) ? KS * KS : ksize * ksize;
-    int32_t* out = table + base * KK;
-    const int total = k * KK;
-    for (int f = lane; f < total; f += 32) {
-        int r = f / KK;
-        int tap = f - r * KK;
-        int dy, dx;
-        tap_to_dydx<KS>(tap, ksize, dy, dx);
-        uint32_t pk = s_pos[wid][r];
-        int p = (int)(pk & 0xFFFFu);
-        int yy = (int)((pk >> 16) & 0xFFu) + dy, xx = (int)(pk >> 24) + dx;
-        int32_t v = -1;
-        if ((unsigned)yy < (unsigned)h && (unsigned)xx < (unsigned)w) {
-            int rk = s_rank[wid][p + dy * w + dx];
-            if (rk >= 0) v = (int32_t)(base + rk);
+    int32_t* so = s_out[wid];
+    for (int r0 = 0; r0 < k; r0 += RR) {
+        const int r = r0 + lane;
+        if (lane < RR && r < k) {
+            const uint32_t pk = s_pos[wid][r];
+            const int p = (int)(pk & 0xFFFFu), y = (int)((pk >> 16) & 0xFFu), x = (int)(pk >> 24);
+            if (KS > 0) {
+#pragma unroll
+                for (int tap = 0; tap < KS * KS; ++tap) {
+                    const int dy = tap / KS - KS / 2, dx = tap % KS - KS / 2;
+                    int32_t v = -1;
+                    if ((unsigned)(y + dy) < (unsigned)h && (unsigned)(x + dx) < (unsigned)w) {
+                        int rk = s_rank[wid][p + dy * w + dx];
+                        if (rk >= 0) v = (int32_t)(base + rk);
+                    }
+                    so[lane * KK + tap] = v;
+                }
+            } else {
+                for (int tap = 0; tap < KK; ++tap) {
+                    const int dy = tap / ksize - ksize / 2, dx = tap % ksize - ksize / 2;
+                    int32_t v = -1;
+                    if ((unsigned)(y + dy) < (unsigned)h && (unsigned)(x + dx) < (unsigned)w) {
+                        int rk = s_rank[wid][p + dy * w + dx];
+                        if (rk >= 0) v = (int32_t)(base + rk);
+                    }
+                    so[lane * KK + tap] = v;
+                }
+            }
         }
-        out[f] = v;
+        __syncwarp();
+        const int rows = (k - r0) < RR ? (k - r0) : RR;
+        const int cnt = rows * KK;
+        const long g0 = (base + r0) * KK;                  // first table element of this round
+        int32_t* out = table + g0;
+        int lead = (int)((4 - (g0 & 3)) & 3);              // scalars up to the next 16-byte boundary
+        if (lead > cnt) lead = cnt;
+        if ((reinterpret_cast<uintptr_t>(table) & 15) != 0) lead = cnt;   // unaligned table: all scalar
+        if (lane < lead) out[lane] = so[lane];
+        const int nvec = (cnt - lead) >> 2;
+        for (int v = lane; v < nvec; v += 32) {
+            const int o = lead + 4 * v;
+            *reinterpret_cast<int4*>(out + o) = make_int4(so[o], so[o + 1], so[o + 2], so[o + 3]);
+        }
+        for (int o = lead + 4 * nvec + lane; o < cnt; o += 32) out[o] = so[o];
+        __syncwarp();
     }
 }
 
@@ -369,12 +413,13 @@ static int table_build_impl(const float* scores, int n_seg, int seg_len, int k, 
     cudaStream_t s = (cudaStream_t)stream;
     if (seg_len <= 256) {
         unsigned grid = (unsigned)((n_seg + 7) / 8);
+        const uint32_t mw = (uint32_t)((0x100000000ull + w - 1) / w), mhw = (uint32_t)((0x100000000ull + h * w - 1) / (h * w));
         if (ksize == 3)
-            table_build_warp_kernel<8, 3><<<grid, 256, 0, s>>>(scores, n_seg, seg_len, k, h, w, ksize, kept_idx, table, idx64);
+            table_build_warp_kernel<8, 3><<<grid, 256, 0, s>>>(scores, n_seg, seg_len, k, h, w, ksize, mw, mhw, kept_idx, table, idx64);
         else if (ksize == 5)
-            table_build_warp_kernel<8, 5><<<grid, 256, 0, s>>>(scores, n_seg, seg_len, k, h, w, ksize, kept_idx, table, idx64);
+            table_build_warp_kernel<8, 5><<<grid, 256, 0, s>>>(scores, n_seg, seg_len, k, h, w, ksize, mw, mhw, kept_idx, table, idx64);
         else
-            table_build_warp_kernel<8, 0><<<grid, 256, 0, s>>>(scores, n_seg, seg_len, k, h, w, ksize, kept_idx, table, idx64);
+            table_build_warp_kernel<8, 0><<<grid, 256, 0, s>>>(scores, n_seg, seg_len, k, h, w, ksize, mw, mhw, kept_idx, table, idx64);
         SV_LAUNCH_CHECK("table_build_warp_kernel");
         return SVTAD_OK;
     }
