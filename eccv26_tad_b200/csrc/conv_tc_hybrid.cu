@@ -283,7 +283,7 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     TmaTail* tail = reinterpret_cast<TmaTail*>(smem + (size_t)nstage * STAGE_BYTES);
-    int* s_idx = reinterpret_cast<int*>(tail + 1);                 // [A_WARPS][2][TILE_M] gather rows of a stage
+    int* s_idx = reinterpret_cast<int*>(tail + 1);                 // per producer warp: [2][STAGE_K * kk] table rows + [TILE_M] gather rows
     volatile int* s_abort = &tail->abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -339,58 +339,85 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
             tap[h] = real ? blk / cblocks : 0;
             ch0[h] = real ? (blk % cblocks) * 64 : 0;
         }
-        int* my_idx = s_idx + warp * 2 * TILE_M;
-        // gather rows of stage `sit` for slots lane*4 .. lane*4+3 (slot = block * 64 + token)
-        auto fetch = [&](int sit, int (&dst)[4]) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int slot = lane * 4 + j;
-                const int h = slot >> 6;
-                long i = i_begin + (long)sit * STAGE_K + (slot & 63);
-                int v = -1;
-                if ((h == 0 || second_real) && i < i_end) {
-                    int raw = __ldg(nbr + i * kk + tap[h]);
-                    long jj = (long)raw + (tpb > 0 ? (i / tpb) * (long)tpb : 0);
-                    if (raw >= 0 && jj < n) v = (int)jj;
-                }
-                dst[j] = v;
-            }
-        };
+        // table rows of a warp's 64-token step, double buffered: [2][STAGE_K * kk] ints per warp
+        const int tab_ints = STAGE_K * kk;
+        int* my_tab = s_idx + warp * (2 * tab_ints + TILE_M);
+        int* my_rows = my_tab + 2 * tab_ints;              // [TILE_M] final gather rows of the current step
         const int sub = lane & 7, rg = lane >> 3;
         // CTAs of different block pairs walk the token range from different starting points (see the
         // forward kernel); `src_stage` is the 64-token step that pipeline step `it` carries
         const int rot = (rotate && total_stages > 0) ? (int)(((long)blockIdx.x * 5) % total_stages) : 0;
         auto src_stage = [&](int it) { int v = it + rot; return v >= total_stages ? v - total_stages : v; };
-        int nxt[4] = {-1, -1, -1, -1};
-        if (warp < total_stages) fetch(src_stage(warp), nxt);
+        // the step's table rows are contiguous in memory: copy them whole (16-byte cp.async, rows past the
+        // end of this split read as zero bytes) one warp-iteration ahead; only these copies are committed
+        auto load_rows = [&](int sit, int buf) {
+            const long i0 = i_begin + (long)sit * STAGE_K;
+            const long rows = (i_end - i0) < STAGE_K ? (i_end - i0) : STAGE_K;
+            const int valid_bytes = (int)rows * kk * 4;
+            const char* src = reinterpret_cast<const char*>(nbr + i0 * kk);
+            const uint32_t dst = smem_u32(my_tab + buf * tab_ints);
+            for (int c = lane; c * 16 < tab_ints * 4; c += 32) {
+                int left = valid_bytes - c * 16;
+                uint32_t nb = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
+                cp_async16(dst + c * 16, nb ? src + c * 16 : src, nb);
+            }
+            cp_async_commit();
+        };
+        if (warp < total_stages) load_rows(src_stage(warp), 0);
         int local = 0;
         int s = warp % nstage;
         uint32_t ph = ((warp / nstage) & 1) ^ 1;
+        const int rows = second_real ? 32 : 16;            // slots 64..127 belong to the second block
         for (int it = warp; it < total_stages; it += A_WARPS, ++local) {
-            int* idx = my_idx + (local & 1) * TILE_M;
-            *reinterpret_cast<int4*>(idx + lane * 4) = make_int4(nxt[0], nxt[1], nxt[2], nxt[3]);
+            const int* tab = my_tab + (local & 1) * tab_ints;
+            cp_async_wait<0>();
             __syncwarp();
-            if (it + A_WARPS < total_stages) fetch(src_stage(it + A_WARPS), nxt);
+            if (it + A_WARPS < total_stages) load_rows(src_stage(it + A_WARPS), (local & 1) ^ 1);
+            // each lane turns four slots (slot = block * 64 + token) into final gather rows, the warp shares them
+            // through shared memory, and every lane then holds the rows of the 32 slots it copies
+            const long i0 = i_begin + (long)src_stage(it) * STAGE_K;
+            {
+                int v4[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int slot = lane * 4 + j;
+                    const int h = slot >> 6, t = slot & 63;
+                    const long i = i0 + t;
+                    int v = -1;
+                    if ((h == 0 || second_real) && i < i_end) {
+                        const int raw = tab[t * kk + tap[h]];
+                        const long jj = (long)raw + (tpb > 0 ? (i / tpb) * (long)tpb : 0);
+                        if (raw >= 0 && jj < n) v = (int)jj;
+                    }
+                    v4[j] = v;
+                }
+                *reinterpret_cast<int4*>(my_rows + lane * 4) = make_int4(v4[0], v4[1], v4[2], v4[3]);
+            }
+            __syncwarp();
+            int jrow[32];
+#pragma unroll
+            for (int itr = 0; itr < 32; ++itr) jrow[itr] = my_rows[itr * 4 + rg];
+            __syncwarp();
             if (!warp_wait(smem_u32(&tail->empty[s]), ph, s_abort, err, 51, lane)) break;
             const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
             const uint32_t bar = smem_u32(&tail->full[s]);
             if (lane == 0) {
                 const uint32_t b_tile = a_tile + A_TILE_BYTES;
-                const int i0 = (int)(i_begin + (long)src_stage(it) * STAGE_K);
                 mbar_expect_tx(bar, B_TILE_BYTES);
 #pragma unroll
                 for (int b = 0; b < B_TILE_BYTES / 8192; ++b)
-                    tma_load_2d(b_tile + b * 8192, &map_gy, n0 + b * 64, i0, bar);
+                    tma_load_2d(b_tile + b * 8192, &map_gy, n0 + b * 64, (int)i0, bar);
             }
-            const int rows = second_real ? 32 : 16;        // rows 64..127 belong to the second block
-#pragma unroll 8
-            for (int itr = 0; itr < rows; ++itr) {
-                const int r = itr * 4 + rg;
-                const int j = idx[r];
-                const int r7 = ((itr & 1) << 2) | rg;
-                const uint32_t dst = a_tile + r * 128 + ((sub ^ r7) << 4);
-                const uint16_t* src = x + (long)(j < 0 ? 0 : j) * cin + ch0[r >> 6] + sub * 8;
-                cp_async16(dst, src, j < 0 ? 0u : 16u);
+#pragma unroll
+            for (int itr = 0; itr < 32; ++itr) {
+                if (itr < rows) {
+                    const int r = itr * 4 + rg;
+                    const int j = jrow[itr];
+                    const int r7 = ((itr & 1) << 2) | rg;
+                    const uint32_t dst = a_tile + r * 128 + ((sub ^ r7) << 4);
+                    const uint16_t* src = x + (long)(j < 0 ? 0 : j) * cin + ch0[itr >> 4] + sub * 8;
+                    cp_async16(dst, src, j < 0 ? 0u : 16u);
+                }
             }
             cp_async_arrive_noinc(bar);
             s += A_WARPS;
@@ -581,9 +608,11 @@ static int launch_wgrad_hybrid(const void* gy, const void* x, const int32_t* nbr
         if (rc) return rc;
     }
     const size_t stage = A_TILE_BYTES + b_tile_bytes_for(BN);
-    const size_t extra = sizeof(TmaTail) + (size_t)A_WARPS * 2 * TILE_M * sizeof(int);
+    const size_t extra = sizeof(TmaTail) + (size_t)A_WARPS * (2 * STAGE_K * kk + TILE_M) * sizeof(int);
     int nstage = (int)((TC_SMEM_LIMIT - 1024 - extra) / stage);
     if (nstage > 8) nstage = 8;
+    if (nstage < 2)
+        return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core wgrad: not enough shared memory for BN=%d kk=%d", BN, kk);
     const size_t smem = 1024 + nstage * stage + extra;
     const bool cluster = pl.cluster && (size_t)TILE_M * (BN + 4) * sizeof(float) <= nstage * stage;
     dim3 grid((unsigned)(pl.n_pairs * pl.n_nblk), (unsigned)pl.splits);
