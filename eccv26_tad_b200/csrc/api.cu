@@ -84,8 +84,8 @@ extern "C" int svtad_conv_fwd(const void* x, const int32_t* nbr, const void* w, 
     if (rc) return rc;
     if (n == 0) return SVTAD_OK;
     SV_CHECK_ARG(x && nbr && w && y, "svtad_conv_fwd: null pointer");
-    SV_CHECK_ARG(aligned(x, 16) && aligned(w, 16) && aligned(y, 16) && aligned(nbr, 4),
-                 "svtad_conv_fwd: x, w and y must be 16-byte aligned");
+    SV_CHECK_ARG(aligned(x, 16) && aligned(w, 16) && aligned(y, 16) && aligned(nbr, 16) && aligned(bias, 16),
+                 "svtad_conv_fwd: x, nbr, w, bias and y must be 16-byte aligned");
     ConvArgs p{x, nbr, w, bias, y, n, cin, cout, kk, tokens_per_batch, dtype};
     if (use_tc(SVTAD_OP_FWD, n, cin, cout, kk, dtype)) return tc_fwd(p, (cudaStream_t)stream);
     if (forced_path() == 2)
@@ -101,8 +101,8 @@ extern "C" int svtad_conv_dgrad(const void* gy, const int32_t* nbr, const void* 
     if (rc) return rc;
     if (n == 0) return SVTAD_OK;
     SV_CHECK_ARG(gy && nbr && w && gx, "svtad_conv_dgrad: null pointer");
-    SV_CHECK_ARG(aligned(gy, 16) && aligned(w, 16) && aligned(gx, 16),
-                 "svtad_conv_dgrad: gy, w and gx must be 16-byte aligned");
+    SV_CHECK_ARG(aligned(gy, 16) && aligned(w, 16) && aligned(gx, 16) && aligned(nbr, 16),
+                 "svtad_conv_dgrad: gy, nbr, w and gx must be 16-byte aligned");
     if (cout % 4 != 0)
         return set_error(SVTAD_ERR_UNSUPPORTED, "svtad_conv_dgrad: C_out (%d) must be divisible by 4", cout);
     cudaStream_t s = (cudaStream_t)stream;
@@ -138,8 +138,8 @@ extern "C" int svtad_conv_wgrad(const void* gy, const void* x, const int32_t* nb
         return SVTAD_OK;
     }
     SV_CHECK_ARG(gy && x && nbr, "svtad_conv_wgrad: null pointer");
-    SV_CHECK_ARG(aligned(gy, 16) && aligned(x, 16) && aligned(gw, 16),
-                 "svtad_conv_wgrad: gy, x and gw must be 16-byte aligned");
+    SV_CHECK_ARG(aligned(gy, 16) && aligned(x, 16) && aligned(gw, 16) && aligned(nbr, 16),
+                 "svtad_conv_wgrad: gy, x, nbr and gw must be 16-byte aligned");
     SV_CHECK_ARG(workspace != nullptr && aligned(workspace, 256), "svtad_conv_wgrad: workspace is null or not 256-byte aligned");
     if (use_tc(SVTAD_OP_WGRAD, n, cin, cout, kk, dtype))
         return tc_wgrad(gy, x, nbr, gw, gb, n, cin, cout, kk, tokens_per_batch, dtype, workspace, workspace_bytes, s);

@@ -237,9 +237,19 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         float b8[8];
+                        if (!DGRAD && bias != nullptr) {
+                            // eight bias values in one 16-byte load (same address for the whole warp)
+                            const uint4 bw = __ldg(reinterpret_cast<const uint4*>(bias + n0 + cbase + g * 8));
+                            const uint32_t w4[4] = {bw.x, bw.y, bw.z, bw.w};
 #pragma unroll
-                        for (int e = 0; e < 8; ++e)
-                            b8[e] = (!DGRAD && bias != nullptr) ? widen(__ldg(bias + n0 + cbase + g * 8 + e), fp16 != 0) : 0.f;
+                            for (int e = 0; e < 4; ++e) {
+                                b8[2 * e] = widen((uint16_t)(w4[e] & 0xFFFFu), fp16 != 0);
+                                b8[2 * e + 1] = widen((uint16_t)(w4[e] >> 16), fp16 != 0);
+                            }
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) b8[e] = 0.f;
+                        }
                         uint4 o;
                         o.x = pack2(__uint_as_float(v[g * 8 + 0]) + b8[0], __uint_as_float(v[g * 8 + 1]) + b8[1], fp16 != 0);
                         o.y = pack2(__uint_as_float(v[g * 8 + 2]) + b8[2], __uint_as_float(v[g * 8 + 3]) + b8[3], fp16 != 0);

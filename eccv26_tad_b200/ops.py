@@ -32,10 +32,18 @@ def _ptr(t):
     return t.data_ptr() if t is not None and t.numel() > 0 else None
 
 
+def _c16(t):
+    """Contiguous and 16-byte aligned (a contiguous slice of a larger tensor may start anywhere)."""
+    t = t.contiguous()
+    if t.numel() and t.data_ptr() % 16:
+        t = t.clone()
+    return t
+
+
 def _i32_table(nbr):
     if nbr.dtype != torch.int32:
         nbr = nbr.to(torch.int32)
-    return nbr.contiguous()
+    return _c16(nbr)
 
 
 def _workspace(op, n, cin, cout, kk, code, device):
@@ -115,8 +123,8 @@ def conv_fwd(x, nbr, weight, bias=None, tokens_per_batch=0):
     _require_cuda(x, nbr, weight, bias)
     code = _dtype_code(x)
     kk, cin, cout = weight.shape
-    x = x.contiguous()
-    weight = weight.contiguous()
+    x = _c16(x)
+    weight = _c16(weight)
     nbr = _i32_table(nbr)
     n = x.numel() // cin if cin else 0
     if weight.dtype != x.dtype or (bias is not None and bias.dtype != x.dtype):
@@ -124,7 +132,7 @@ def conv_fwd(x, nbr, weight, bias=None, tokens_per_batch=0):
     out = torch.empty((n, cout), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
         _lib.check(_lib.load().svtad_conv_fwd(_ptr(x), _ptr(nbr), _ptr(weight),
-                                              _ptr(bias.contiguous()) if bias is not None else None,
+                                              _ptr(_c16(bias)) if bias is not None else None,
                                               _ptr(out), n, cin, cout, kk, tokens_per_batch, code,
                                               None, 0, _stream()))
     return out
@@ -135,8 +143,8 @@ def conv_dgrad(gy, nbr, weight, tokens_per_batch=0, table_status=None, assume_sy
     _require_cuda(gy, nbr, weight)
     code = _dtype_code(gy)
     kk, cin, cout = weight.shape
-    gy = gy.contiguous()
-    weight = weight.contiguous()
+    gy = _c16(gy)
+    weight = _c16(weight)
     nbr = _i32_table(nbr)
     n = gy.numel() // cout
     if weight.dtype != gy.dtype:
@@ -159,8 +167,8 @@ def conv_wgrad(gy, x, nbr, kk, tokens_per_batch=0, with_bias=True):
     code = _dtype_code(x)
     cin = x.shape[-1]
     cout = gy.shape[-1]
-    gy = gy.contiguous()
-    x = x.contiguous()
+    gy = _c16(gy)
+    x = _c16(x)
     nbr = _i32_table(nbr)
     n = x.numel() // cin
     if gy.dtype != x.dtype:
