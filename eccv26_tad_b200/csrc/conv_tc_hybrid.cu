@@ -85,6 +85,22 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
         fence_mbar_init();
         tma_prefetch_map(&map_w);
     }
+    // raw table rows of a tile -> s_tab[buf], by the producer threads, one tile ahead
+    auto load_table = [&](int tile, int buf) {
+        const long row0 = (long)(tile / n_blks) * TILE_M;
+        const long rows = (n - row0) < TILE_M ? (n - row0) : TILE_M;
+        const int valid_bytes = (int)rows * kk * 4;
+        const char* src = reinterpret_cast<const char*>(nbr + row0 * kk);
+        const uint32_t dst = smem_u32(s_tab + buf * tab_ints);
+        for (int c = tid; c * 16 < tab_ints * 4; c += A_THREADS) {
+            int left = valid_bytes - c * 16;
+            uint32_t nb = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
+            cp_async16(dst + c * 16, nb ? src + c * 16 : src, nb);
+        }
+        cp_async_commit();
+    };
+    // the first tile's rows start their trip while the barriers and the tensor memory are set up
+    if (warp < A_WARPS && (int)blockIdx.x < tiles_total) load_table(blockIdx.x, 0);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -92,23 +108,9 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
 
     if (warp < A_WARPS) {
         // ------------------------------------------------------------------ producers
-        auto load_table = [&](int tile, int buf) {
-            const long row0 = (long)(tile / n_blks) * TILE_M;
-            const long rows = (n - row0) < TILE_M ? (n - row0) : TILE_M;
-            const int valid_bytes = (int)rows * kk * 4;
-            const char* src = reinterpret_cast<const char*>(nbr + row0 * kk);
-            const uint32_t dst = smem_u32(s_tab + buf * tab_ints);
-            for (int c = tid; c * 16 < tab_ints * 4; c += A_THREADS) {
-                int left = valid_bytes - c * 16;
-                uint32_t nb = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
-                cp_async16(dst + c * 16, nb ? src + c * 16 : src, nb);
-            }
-            cp_async_commit();
-        };
         const int sub = lane & 7, rg = lane >> 3;
         bool alive = true;
         int local = 0;
-        if ((int)blockIdx.x < tiles_total) load_table(blockIdx.x, 0);
         for (int tile = blockIdx.x; tile < tiles_total; tile += gridDim.x, ++local) {
             const int buf = local & 1;
             const long row0 = (long)(tile / n_blks) * TILE_M;
