@@ -220,43 +220,43 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
         }
     } else {
         // ------------------------------------------------------------------ epilogue (warps 5..8)
+        constexpr int NC = BN / 32;
         const int q = warp & 3;
+        const int et = tid - (A_WARPS + 1) * 32;          // 0..127 among the epilogue threads
+        float* s_bias = reinterpret_cast<float*>(s_tab + 2 * tab_ints);   // [2][256]
         int local = 0;
         for (int tile = blockIdx.x; tile < tiles_total; tile += gridDim.x, ++local) {
             const int buf = local & 1;
             const long row = (long)(tile / n_blks) * TILE_M + q * 32 + lane;
             const int n0 = (tile % n_blks) * BN;
+            // the tile's bias goes to shared memory while the main loop is still running
+            float* sb = s_bias + buf * 256;
+            for (int t = et; t < BN; t += 128)
+                sb[t] = (!DGRAD && bias != nullptr) ? widen(__ldg(bias + n0 + t), fp16 != 0) : 0.f;
+            named_bar_sync(2, 128);
             if (!mbar_wait(smem_u32(&tail->accum_full[buf]), (local >> 1) & 1, s_abort, err, 44)) break;
             tc_fence_after();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-#pragma unroll 1
-            for (int cbase = 0; cbase < BN; cbase += 32) {
-                uint32_t v[32];
-                tmem_ld32(t_addr + cbase, v);
+            uint16_t* orow = out + row * cn + n0;
+            // two 32-column chunks in flight: the next tcgen05.ld runs while this chunk is converted and stored
+            uint32_t va[32], vb[32];
+            tmem_ld32(t_addr, va);
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                uint32_t (&v)[32] = (c & 1) ? vb : va;
                 tmem_ld_wait();
+                if (c + 1 < NC) tmem_ld32(t_addr + (c + 1) * 32, (c & 1) ? va : vb);
                 if (row < n) {
-                    uint4* dst = reinterpret_cast<uint4*>(out + row * cn + n0 + cbase);
+                    uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+                    const float4* b4 = reinterpret_cast<const float4*>(sb + c * 32);
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
-                        float b8[8];
-                        if (!DGRAD && bias != nullptr) {
-                            // eight bias values in one 16-byte load (same address for the whole warp)
-                            const uint4 bw = __ldg(reinterpret_cast<const uint4*>(bias + n0 + cbase + g * 8));
-                            const uint32_t w4[4] = {bw.x, bw.y, bw.z, bw.w};
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                b8[2 * e] = widen((uint16_t)(w4[e] & 0xFFFFu), fp16 != 0);
-                                b8[2 * e + 1] = widen((uint16_t)(w4[e] >> 16), fp16 != 0);
-                            }
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) b8[e] = 0.f;
-                        }
+                        const float4 ba = b4[2 * g], bb = b4[2 * g + 1];
                         uint4 o;
-                        o.x = pack2(__uint_as_float(v[g * 8 + 0]) + b8[0], __uint_as_float(v[g * 8 + 1]) + b8[1], fp16 != 0);
-                        o.y = pack2(__uint_as_float(v[g * 8 + 2]) + b8[2], __uint_as_float(v[g * 8 + 3]) + b8[3], fp16 != 0);
-                        o.z = pack2(__uint_as_float(v[g * 8 + 4]) + b8[4], __uint_as_float(v[g * 8 + 5]) + b8[5], fp16 != 0);
-                        o.w = pack2(__uint_as_float(v[g * 8 + 6]) + b8[6], __uint_as_float(v[g * 8 + 7]) + b8[7], fp16 != 0);
+                        o.x = pack2(__uint_as_float(v[g * 8 + 0]) + ba.x, __uint_as_float(v[g * 8 + 1]) + ba.y, fp16 != 0);
+                        o.y = pack2(__uint_as_float(v[g * 8 + 2]) + ba.z, __uint_as_float(v[g * 8 + 3]) + ba.w, fp16 != 0);
+                        o.z = pack2(__uint_as_float(v[g * 8 + 4]) + bb.x, __uint_as_float(v[g * 8 + 5]) + bb.y, fp16 != 0);
+                        o.w = pack2(__uint_as_float(v[g * 8 + 6]) + bb.z, __uint_as_float(v[g * 8 + 7]) + bb.w, fp16 != 0);
                         dst[g] = o;
                     }
                 }
@@ -573,7 +573,7 @@ static int launch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaStre
         if (rc) return rc;
     }
     const size_t stage = A_TILE_BYTES + b_tile_bytes_for(BN);
-    const size_t extra = sizeof(TmaTail) + 2 * (size_t)TILE_M * p.kk * sizeof(int);
+    const size_t extra = sizeof(TmaTail) + 2 * (size_t)TILE_M * p.kk * sizeof(int) + 2 * 256 * sizeof(float);
     int nstage = (int)((TC_SMEM_LIMIT - 1024 - extra) / stage);
     if (nstage > 8) nstage = 8;
     if (nstage < 2)
