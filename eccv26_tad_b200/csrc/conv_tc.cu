@@ -198,6 +198,7 @@ wgrad_reduce4_kernel(const float* __restrict__ ws_w, int splits, const float* __
         return;
     }
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
     for (int s = 0; s < cnt; ++s) {
         float4 v = __ldcg(reinterpret_cast<const float4*>(src + (long)s * stride));
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;

@@ -483,22 +483,26 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
             if (CLUSTER) dstrow = nullptr;
             // cluster mode: the tile is parked in this CTA's (now idle) stage ring, row stride BN + 4 floats
             float* stage_row = reinterpret_cast<float*>(smem) + (q * 32 + lane) * (BN + 4);
-#pragma unroll 1
-            for (int cbase = 0; cbase < BN; cbase += 32) {
-                uint32_t v[32];
+            constexpr int NC = BN / 32;
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+            uint32_t va[32], vb[32];
+            if (total_stages > 0) tmem_ld32(t_addr, va);
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                uint32_t (&v)[32] = (c & 1) ? vb : va;
                 if (total_stages > 0) {
-                    tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + cbase, v);
                     tmem_ld_wait();
+                    if (c + 1 < NC) tmem_ld32(t_addr + (c + 1) * 32, (c & 1) ? va : vb);
                 } else {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = 0u;
                 }
                 if (CLUSTER) {
-                    uint4* dst = reinterpret_cast<uint4*>(stage_row + cbase);
+                    uint4* dst = reinterpret_cast<uint4*>(stage_row + c * 32);
 #pragma unroll
                     for (int g = 0; g < 8; ++g) dst[g] = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
                 } else if (dstrow != nullptr) {
-                    uint4* dst = reinterpret_cast<uint4*>(dstrow + cbase);
+                    uint4* dst = reinterpret_cast<uint4*>(dstrow + c * 32);
 #pragma unroll
                     for (int g = 0; g < 8; ++g) dst[g] = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
                 }
