@@ -231,6 +231,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying CUDA graphs")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-ref-cuda", action="store_true")
+    ap.add_argument("--workload", default="sparseconv", choices=["sparseconv", "backbone"],
+                    help="backbone: forward of the ViT-B sparse-adapter backbone on 160-frame clips (secondary line)")
     ap.add_argument("--kernel-case", default=None, choices=["fwd", "dgrad", "wgrad", "table"],
                     help="profiling aid: launch only this kernel a few times on --case-slices slices and exit")
     ap.add_argument("--case-slices", type=int, default=3840)
@@ -240,6 +242,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.kernel_case:
         return kernel_case(args)
+    if args.workload == "backbone":
+        return backbone_case(args)
     if args.impl == "reference":
         return reference_arm(args)
 
@@ -521,6 +525,56 @@ def main():
         dist.barrier()
         sys.stdout.flush()
         sys.stderr.flush()
+        os._exit(0)
+
+
+def backbone_case(args):
+    """Secondary measurement: forward of the sparse-adapter ViT-B backbone, bf16, random-init weights, one 3x160x224x224
+    clip per step and rank (clips are sharded over ranks; no collective in the forward), 30 % keep after block 3."""
+    import torch
+    import torch.distributed as dist
+    from eccv26_tad_b200 import SparseAdapterViT
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    torch.manual_seed(5 + rank)
+    model = SparseAdapterViT().to(dev).eval()
+    for blk in model.blocks:
+        torch.nn.init.normal_(blk.adapter.up_proj.weight, std=0.02)
+    clips = [torch.randn(1, 3, 160, 224, 224, device=dev) for _ in range(2)]
+    steps, warm = max(1, min(args.steps, 20)), max(3, min(args.warmup, 5))
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        for i in range(warm):
+            model(clips[i % 2])
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(steps):
+            out = model(clips[i % 2])
+        b.record()
+        torch.cuda.synchronize()
+    ms = a.elapsed_time(b)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        print(json.dumps({"metric": "sparse-adapter ViT-B backbone forward, clips/s", "value": world * steps / (ms * 1e-3),
+                          "unit": "clips/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms / steps,
+                          "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": "ViT-B/16 sparse-adapter backbone forward, 3x160x224x224 clips, "
+                                                 "15680 tokens + CLS, adapters 768->192->768 with SparseConv2D 3x3, keep 30 % after block 3"},
+                          "out_shape": list(out.shape)}))
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
         os._exit(0)
 
 

@@ -7,3 +7,4 @@ from .neighbor_table import (  # noqa: F401
     select_topk,
     update_neighbor_indices,
 )
+from .backbone import SparseAdapterViT  # noqa: F401,E402

@@ -1,0 +1,61 @@
+"""Sparse-adapter ViT backbone (the config-5 family at reduced size).
+
+CPU: the dense restatement (scatter -> conv2d -> gather adapters, torch table code) runs and has the
+reference's output shape.  GPU: the product path (SparseConv2d + CUDA table kernels) gives the same
+features as the dense restatement with the same weights, in fp32 and under bf16 autocast.
+"""
+import pytest
+import torch
+
+from eccv26_tad_b200.backbone import SparseAdapterViT, sinusoid_table
+
+CFG = dict(img_size=64, patch_size=16, tubelet_size=2, num_frames=8, embed_dims=128, depth=4, num_heads=4,
+           adapter_dims=64, keep_rates=[1.0, 0.5, 1.0, 0.6])
+
+
+def _models(device, **over):
+    torch.manual_seed(0)
+    cfg = dict(CFG, **over)
+    dense = SparseAdapterViT(conv_impl="dense", table_impl="torch", **cfg)
+    for blk in dense.blocks:   # the reference zero-initialises up_proj; make the adapters matter
+        torch.nn.init.normal_(blk.adapter.up_proj.weight, std=0.05)
+    dense = dense.to(device).eval()
+    sparse = SparseAdapterViT(conv_impl="svtad", table_impl="svtad", **cfg).to(device).eval()
+    sparse.load_state_dict(dense.state_dict())
+    return dense, sparse
+
+
+def test_dense_restatement_runs_on_cpu():
+    dense, _ = _models("cpu")
+    video = torch.randn(2, 3, 8, 64, 64)
+    with torch.no_grad():
+        out = dense(video)
+    assert out.shape == (2, 128, 4 + 1) and torch.isfinite(out).all()
+    assert sinusoid_table(10, 8).shape == (1, 10, 8)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("autocast", [False, True])
+def test_sparse_path_matches_dense_restatement(autocast):
+    # Under bf16 the two models' scores differ in the last bits once an adapter has run, and a top-k at a near-tie
+    # would pick different tokens; so the bf16 case selects once, in the first block, where both see the same bits.
+    dense, sparse = _models("cuda", **({"keep_rates": [0.5, 1.0, 1.0, 1.0]} if autocast else {}))
+    video = torch.randn(3, 3, 8, 64, 64, device="cuda")
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16, enabled=autocast):
+        a = dense(video).float()
+        b = sparse(video).float()
+    err = (a - b).abs().max().item() / a.abs().max().item()
+    assert err < (3e-2 if autocast else 1e-4), err
+
+
+@pytest.mark.gpu
+def test_backbone_backward_reaches_adapter_parameters():
+    _, sparse = _models("cuda")
+    sparse.train()
+    video = torch.randn(2, 3, 8, 64, 64, device="cuda")
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        out = sparse(video)
+    out.float().square().mean().backward()
+    for blk in sparse.blocks:
+        g = blk.adapter.sparse_conv.weight.grad
+        assert g is not None and torch.isfinite(g).all() and g.abs().sum() > 0
