@@ -46,6 +46,15 @@ def _i32_table(nbr):
     return _c16(nbr)
 
 
+def _check_shapes(who, n, kk, nbr, **feat):
+    """The C library trusts its sizes; mismatched tensors are caught here."""
+    if nbr.numel() != n * kk:
+        raise ValueError(f"{who}: neighbor table has {nbr.numel()} entries, expected {n} rows x {kk} taps")
+    for name, (t, cols) in feat.items():
+        if t is not None and t.numel() != n * cols:
+            raise ValueError(f"{who}: {name} has {t.numel()} elements, expected {n} x {cols}")
+
+
 def _workspace(op, n, cin, cout, kk, code, device):
     nbytes = _lib.load().svtad_workspace_bytes(op, n, cin, cout, kk, code)
     if nbytes == 0:
@@ -129,6 +138,9 @@ def conv_fwd(x, nbr, weight, bias=None, tokens_per_batch=0):
     n = x.numel() // cin if cin else 0
     if weight.dtype != x.dtype or (bias is not None and bias.dtype != x.dtype):
         raise ValueError("x, weight and bias must share one dtype")
+    _check_shapes("conv_fwd", n, kk, nbr)
+    if bias is not None and bias.numel() != cout:
+        raise ValueError(f"conv_fwd: bias has {bias.numel()} elements, expected {cout}")
     out = torch.empty((n, cout), dtype=x.dtype, device=x.device)
     with torch.cuda.device(x.device):
         _lib.check(_lib.load().svtad_conv_fwd(_ptr(x), _ptr(nbr), _ptr(weight),
@@ -149,6 +161,7 @@ def conv_dgrad(gy, nbr, weight, tokens_per_batch=0, table_status=None, assume_sy
     n = gy.numel() // cout
     if weight.dtype != gy.dtype:
         raise ValueError("grad_output and weight must share one dtype")
+    _check_shapes("conv_dgrad", n, kk, nbr)
     gx = torch.empty((n, cin), dtype=gy.dtype, device=gy.device)
     with torch.cuda.device(gy.device):
         if assume_symmetric:
@@ -173,6 +186,7 @@ def conv_wgrad(gy, x, nbr, kk, tokens_per_batch=0, with_bias=True):
     n = x.numel() // cin
     if gy.dtype != x.dtype:
         raise ValueError("grad_output and x must share one dtype")
+    _check_shapes("conv_wgrad", n, kk, nbr, grad_output=(gy, cout))
     gw = torch.empty((kk, cin, cout), dtype=x.dtype, device=x.device)
     gb = torch.empty((cout,), dtype=x.dtype, device=x.device) if with_bias else None
     with torch.cuda.device(x.device):

@@ -87,3 +87,14 @@ def test_module_surface_matches_reference():
     from eccv26_tad_b200 import opentad_sparse_ops as shim
     for name in ("fwd", "bwd_in", "bwd_w", "implicit_gemm_fwd_v2", "implicit_gemm_fwd_v2_chunked"):
         assert callable(getattr(shim, name))
+
+
+def test_shape_mismatches_raise_before_any_launch():
+    import torch
+    from eccv26_tad_b200 import ops
+    nbr = torch.zeros(5, 9, dtype=torch.int32)
+    with pytest.raises(ValueError):
+        ops._check_shapes("conv_fwd", 4, 9, nbr)
+    with pytest.raises(ValueError):
+        ops._check_shapes("conv_wgrad", 5, 9, nbr, grad_output=(torch.zeros(4, 8), 8))
+    ops._check_shapes("conv_wgrad", 5, 9, nbr, grad_output=(torch.zeros(5, 8), 8))
