@@ -4,6 +4,7 @@ from .neighbor_table import (  # noqa: F401
     build_neighbor_table,
     get_initial_neighbor_indices,
     num_keep_tokens,
+    select_and_update,
     select_topk,
     update_neighbor_indices,
 )

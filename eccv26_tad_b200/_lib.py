@@ -24,6 +24,7 @@ SIGNATURES = {
     "svtad_table_build": (c_int, [c_p, c_int, c_int, c_int, c_int, c_int, c_int, c_p, c_p, c_p]),
     "svtad_topk_select": (c_int, [c_p, c_int, c_int, c_int, c_p, c_p]),
     "svtad_table_remap": (c_int, [c_p, c_p, c_int, c_int, c_int, c_int, c_p, c_p, c_p]),
+    "svtad_table_select_remap": (c_int, [c_p, c_p, c_int, c_int, c_int, c_int, c_p, c_p, c_p, c_p]),
     "svtad_table_check": (c_int, [c_p, c_i64, c_int, c_int, c_p, c_p]),
     "svtad_workspace_bytes": (c_sz, [c_int, c_i64, c_int, c_int, c_int, c_int]),
     "svtad_conv_fwd": (c_int, [c_p, c_p, c_p, c_p, c_p, c_i64, c_int, c_int, c_int, c_int, c_int, c_p, c_sz, c_p]),

@@ -26,7 +26,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .neighbor_table import get_initial_neighbor_indices, num_keep_tokens, select_topk, update_neighbor_indices
+from .neighbor_table import get_initial_neighbor_indices, num_keep_tokens, select_and_update, select_topk
 from .sparse_conv_layer import SparseConv2d
 
 
@@ -52,7 +52,7 @@ class KTPAttention(nn.Module):
         self.proj = nn.Linear(dim, dim)
         self.keep_rate = keep_rate
 
-    def forward(self, x, table_impl="svtad"):
+    def forward(self, x):
         B, N, C = x.shape
         bias = torch.cat((self.q_bias, torch.zeros_like(self.v_bias), self.v_bias))
         qkv = F.linear(x, self.qkv.weight, bias).reshape(B, N, 3, self.num_heads, -1).permute(2, 0, 3, 1, 4)
@@ -64,12 +64,7 @@ class KTPAttention(nn.Module):
         # CLS query against all keys, softmax, summed over the (single) key token, mean over heads (:743-777)
         attn = ((q[:, :, :1] * self.scale) @ k.transpose(-2, -1)).softmax(dim=-1)
         scores = attn.sum(dim=-2).mean(dim=1)[:, 1:].float()
-        k_keep = min(num_keep_tokens(self.keep_rate, N - 1), scores.shape[1])
-        if table_impl == "svtad":
-            idx = select_topk(scores, k_keep)
-        else:
-            idx = torch.topk(scores, k_keep, dim=1, largest=True)[1].sort(dim=1)[0]
-        return out, idx
+        return out, scores
 
 
 class SparseAdapter(nn.Module):
@@ -121,16 +116,26 @@ class Block(nn.Module):
         self.adapter = SparseAdapter(dim, hidden, kernel_size)
         self.keep_rate = keep_rate
 
-    def forward(self, x, grid_idx, table, scratch, h, w, total, conv_impl, table_impl):
-        attn_out, idx = self.attn(self.norm1(x), table_impl)
+    def forward(self, x, grid_idx, table, h, w, total, conv_impl, table_impl):
+        attn_out, scores = self.attn(self.norm1(x))
         x = x + attn_out
-        if idx is not None:
+        if scores is not None:
             C = x.shape[-1]
+            k_keep = min(num_keep_tokens(self.keep_rate, scores.shape[1]), scores.shape[1])
+            new_table = None
+            if table_impl != "svtad":
+                idx = torch.topk(scores, k_keep, dim=1, largest=True)[1].sort(dim=1)[0]
+            elif table is not None:
+                idx, new_table = select_and_update(scores, table, k_keep)    # one kernel for the whole round
+            else:
+                idx = select_topk(scores, k_keep)
             kept = torch.gather(x[:, 1:], 1, idx.unsqueeze(-1).expand(-1, -1, C))
             x = torch.cat([x[:, :1], kept], dim=1)
             grid_idx = torch.gather(grid_idx, 1, idx)
-            if table is not None:
-                table = update_neighbor_indices(table, idx, scratch) if table_impl == "svtad" else _torch_remap(table, idx)
+            if new_table is not None:
+                table = new_table
+            elif table is not None:
+                table = _torch_remap(table, idx)
         x = x + self.mlp(self.norm2(x))
         x = self.adapter(x, grid_idx, table, h, w, total, conv_impl)
         return x, grid_idx, table
@@ -187,12 +192,11 @@ class SparseAdapterViT(nn.Module):
         x = x + self.pos_embed[:, :total].to(x.dtype)
         x = torch.cat([self.cls_token.expand(B, -1, -1).to(x.dtype), x], dim=1)
         grid_idx = torch.arange(total, device=x.device).unsqueeze(0).repeat(B, 1)
-        table = scratch = None
+        table = None
         if self.conv_impl == "svtad":
             table = get_initial_neighbor_indices(h, w, T, x.device, B, self.kernel_size)
-            scratch = torch.empty(B * total, dtype=torch.int32, device=x.device)
         for blk in self.blocks:
-            x, grid_idx, table = blk(x, grid_idx, table, scratch, h, w, total, self.conv_impl, self.table_impl)
+            x, grid_idx, table = blk(x, grid_idx, table, h, w, total, self.conv_impl, self.table_impl)
         x = self.norm(x)
         tokens = x[:, 1:]
         frame = grid_idx // (h * w)

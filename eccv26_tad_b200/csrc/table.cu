@@ -219,7 +219,7 @@ __device__ __forceinline__ int block_excl_scan_flag(bool flag, int* s_w, int& to
 __global__ void __launch_bounds__(BLK)
 table_build_block_kernel(const float* __restrict__ scores, int n_seg, int L, int k, int h, int w,
                          int ksize, int32_t* __restrict__ kept_idx, int32_t* __restrict__ table,
-                         int64_t* __restrict__ idx64) {
+                         int64_t* __restrict__ idx64, const int32_t* __restrict__ table_in, int kk_in) {
     extern __shared__ int32_t s_rank[];          // [L]
     __shared__ int s_hist[256];
     __shared__ int s_w[BLK / 32];
@@ -293,9 +293,30 @@ table_build_block_kernel(const float* __restrict__ scores, int n_seg, int L, int
     __syncthreads();
     if (table == nullptr) return;
 
+    const long base = (long)seg * k;
+    if (table_in != nullptr) {
+        // (3') later pruning round: the kept rows of the previous table, renumbered through the rank array
+        const long total_in = (long)k * kk_in;
+        const long seg0 = (long)seg * L;
+        int32_t* out_r = table + base * kk_in;
+        for (long f = tid; f < total_in; f += BLK) {
+            int r = (int)(f / kk_in);
+            int tap = (int)(f - (long)r * kk_in);
+            int p = __ldcg(pos_out + r);
+            int32_t old = __ldg(table_in + (seg0 + p) * kk_in + tap);
+            int32_t v = -1;
+            long loc = (long)old - seg0;
+            if (old >= 0 && loc >= 0 && loc < L) {
+                int rk = s_rank[loc];
+                if (rk >= 0) v = (int32_t)(base + rk);
+            }
+            out_r[f] = v;
+        }
+        return;
+    }
+
     // (3) emit table rows
     const int KK = ksize * ksize, hw = h * w, r0 = ksize >> 1;
-    const long base = (long)seg * k;
     int32_t* out = table + base * KK;
     const long total = (long)k * KK;
     for (long f = tid; f < total; f += BLK) {
@@ -435,7 +456,7 @@ static int table_build_impl(const float* scores, int n_seg, int seg_len, int k, 
         SV_CUDA(cudaFuncSetAttribute(table_build_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         attr_dev = dev;
     }
-    table_build_block_kernel<<<n_seg, BLK, smem, s>>>(scores, n_seg, seg_len, k, h, w, ksize, kept_idx, table, idx64);
+    table_build_block_kernel<<<n_seg, BLK, smem, s>>>(scores, n_seg, seg_len, k, h, w, ksize, kept_idx, table, idx64, nullptr, 0);
     SV_LAUNCH_CHECK("table_build_block_kernel");
     return SVTAD_OK;
 }
@@ -455,6 +476,24 @@ extern "C" int svtad_topk_select(const float* scores, int n_seg, int seg_len, in
     SV_CHECK_ARG(n_seg == 0 || k_keep == 0 || idx != nullptr, "svtad_topk_select: idx is null");
     return table_build_impl(scores, n_seg, seg_len, k_keep, 0, 0, 0, nullptr, nullptr, idx, stream,
                             "svtad_topk_select");
+}
+
+extern "C" int svtad_table_select_remap(const float* scores, const int32_t* table_in, int B, int n_prev,
+                                        int k_keep, int kk, int32_t* kept_idx, int64_t* idx, int32_t* table_out,
+                                        void* stream) {
+    SV_CHECK_ARG(B >= 0 && n_prev > 0 && kk > 0, "svtad_table_select_remap: bad sizes");
+    SV_CHECK_ARG(k_keep >= 0 && k_keep <= n_prev, "svtad_table_select_remap: k_keep=%d outside [0, %d]", k_keep, n_prev);
+    SV_CHECK_ARG((long)B * n_prev < (1l << 31), "svtad_table_select_remap: row count does not fit int32 indices");
+    if (B == 0 || k_keep == 0) return SVTAD_OK;
+    SV_CHECK_ARG(scores && table_in && kept_idx && table_out, "svtad_table_select_remap: null pointer");
+    size_t smem = (size_t)n_prev * sizeof(int32_t);
+    if (smem > 200 * 1024)
+        return set_error(SVTAD_ERR_UNSUPPORTED, "svtad_table_select_remap: n_prev=%d exceeds the %d-token limit", n_prev, 200 * 1024 / 4);
+    SV_CUDA(cudaFuncSetAttribute(table_build_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    table_build_block_kernel<<<B, BLK, smem, (cudaStream_t)stream>>>(scores, B, n_prev, k_keep, n_prev, 1, 1, kept_idx,
+                                                                     table_out, idx, table_in, kk);
+    SV_LAUNCH_CHECK("table_build_block_kernel");
+    return SVTAD_OK;
 }
 
 extern "C" int svtad_table_remap(const int32_t* table_in, const int64_t* idx, int B, int n_prev,

@@ -37,6 +37,14 @@ def update_neighbor_indices(neighbor_indices, idx, global_mapping_buffer=None):
     return ops.table_remap(neighbor_indices, idx, global_mapping_buffer)
 
 
+def select_and_update(scores, neighbor_indices, num_keep):
+    """``select_topk`` and ``update_neighbor_indices`` of one pruning round fused into one kernel.
+
+    scores float32 ``[B, N_prev]``, neighbor_indices int32 ``[B, N_prev, K*K]`` -> ``(idx int64 [B, k], table)``.
+    """
+    return ops.table_select_remap(scores, neighbor_indices, num_keep)
+
+
 def build_neighbor_table(scores, keep_rate=None, h=14, w=14, kernel_size=3, num_keep=None):
     """Fused first round: top-k per segment straight to ``(kept_idx, table)``.
 

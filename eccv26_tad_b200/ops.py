@@ -114,6 +114,26 @@ def table_remap(table, idx, scratch=None):
     return out
 
 
+def table_select_remap(scores, table, k_keep):
+    """One later pruning round in one kernel: scores float32 [B, N_prev], table int32 [B, N_prev, KK] ->
+    (idx int64 [B, k], table int32 [B, k, KK])."""
+    _require_cuda(scores, table)
+    if scores.dtype != torch.float32:
+        scores = scores.float()
+    scores = scores.contiguous()
+    table = _i32_table(table)
+    B, n_prev, kk = table.shape
+    if tuple(scores.shape) != (B, n_prev):
+        raise ValueError(f"table_select_remap: scores {tuple(scores.shape)} do not match the table's {(B, n_prev)}")
+    kept = torch.empty((B, k_keep), dtype=torch.int32, device=table.device)
+    idx = torch.empty((B, k_keep), dtype=torch.int64, device=table.device)
+    out = torch.empty((B, k_keep, kk), dtype=torch.int32, device=table.device)
+    with torch.cuda.device(table.device):
+        _lib.check(_lib.load().svtad_table_select_remap(_ptr(scores), _ptr(table), B, n_prev, k_keep, kk, _ptr(kept),
+                                                        _ptr(idx), _ptr(out), _stream()))
+    return idx, out
+
+
 def table_check(nbr, tokens_per_batch=0, status=None):
     """Returns a 1-element int32 device tensor: 0 = valid symmetric table (no host sync)."""
     _require_cuda(nbr)

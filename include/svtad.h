@@ -92,6 +92,17 @@ int svtad_table_remap(const int32_t* table_in, const int64_t* idx, int B, int n_
                       int kk, int32_t* scratch, int32_t* table_out, void* stream);
 
 /*
+ * Selection and remap of a later pruning round in one kernel: per batch row, the k_keep largest of
+ * scores float32 [B, n_prev] (tie / NaN rule as above) give kept_idx int32 [B, k_keep] and, if idx is not
+ * NULL, the same positions as int64 [B, k_keep]; table_out int32 [B, k_keep, kk] holds the kept rows of
+ * table_in int32 [B, n_prev, kk] renumbered to B*k_keep global indices.  n_prev <= 51200.
+ * Replaces torch.topk + sort (vit_sparse_adapter_poguise.py:785-787) plus the gather + remap block
+ * (:913-977) of one Block._inner_forward call; needs no mapping buffer.
+ */
+int svtad_table_select_remap(const float* scores, const int32_t* table_in, int B, int n_prev, int k_keep,
+                             int kk, int32_t* kept_idx, int64_t* idx, int32_t* table_out, void* stream);
+
+/*
  * Validates a table on the device: ORs SVTAD_TABLE_OUT_OF_RANGE / SVTAD_TABLE_ASYMMETRIC into
  * status[0] (int32, device memory, cleared by this call first).  "Symmetric" means
  * nbr[nbr[i,k]+off, kk-1-k]+off == i for every valid entry, which every table produced by the

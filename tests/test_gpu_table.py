@@ -116,6 +116,31 @@ def test_remap_chain_matches_golden(golden_dir):
             np.testing.assert_array_equal(table.cpu().numpy(), g[f"{n}_table{r}"])
 
 
+def test_fused_select_remap_chain_matches_golden(golden_dir):
+    """Same schedules as above with selection + remap of a round fused into one kernel."""
+    ops = _ops()
+    g = np.load(os.path.join(golden_dir, "table_chain.npz"))
+    for n in sorted(k[:-4] for k in g.files if k.endswith("_cfg")):
+        h, w, T, B, rounds = (int(v) for v in g[n + "_cfg"])
+        table = ops.table_init(B, T, h, w, 3)
+        for r in range(rounds):
+            scores = torch.from_numpy(g[f"{n}_scores{r}"]).cuda()
+            k = g[f"{n}_idx{r}"].shape[1]
+            idx, table = ops.table_select_remap(scores, table, k)
+            np.testing.assert_array_equal(idx.cpu().numpy(), g[f"{n}_idx{r}"])
+            np.testing.assert_array_equal(table.cpu().numpy(), g[f"{n}_table{r}"])
+    # ties / NaN through the fused path against the oracle
+    rng = np.random.default_rng(9)
+    s = rng.integers(-2, 3, size=(3, 392)).astype(np.float32)
+    s[1, ::5] = np.nan
+    t0 = otab.initial_table(14, 14, 2, 3)
+    for k in (1, 100, 391, 392):
+        idx, tab = ops.table_select_remap(torch.from_numpy(s).cuda(), torch.from_numpy(t0).cuda(), k)
+        eidx = otab.select_topk(s, k)
+        np.testing.assert_array_equal(idx.cpu().numpy(), eidx)
+        np.testing.assert_array_equal(tab.cpu().numpy(), otab.remap_table(t0, eidx))
+
+
 def test_remap_unsorted_and_bad_indices_do_not_fault():
     ops = _ops()
     table = ops.table_init(2, 1, 4, 4, 3)
