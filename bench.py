@@ -19,7 +19,8 @@ Numbers on the JSON line
   e2e          same metric through the public Python surface (build_neighbor_table + SparseConv2d
                forward / backward under autograd) with HOST buffers: every step copies scores,
                features and upstream gradients from pinned host memory and copies the outputs and
-               all gradients back
+               all gradients back; the three keep rates run as three layers on three streams, so
+               copies in, kernels and copies out of different layers overlap
   roofline     the dominant kernel (largest share of device time among forward / dgrad / wgrad),
                dense-equivalent FLOPs 2*N*KK*Cin*Cout per launch over its CUDA-event duration,
                against the measured bf16 peak in MEASURED_PEAKS.json (fallback 1590 TFLOP/s)
@@ -433,59 +434,93 @@ def main():
     }
 
     # ---------------------------------------------------------------- e2e through the public API, host buffers
-    module = SparseConv2d(C, C).to(dev)
+    # One SparseConv2d per keep rate (three adapter layers with the same initial weights), each on its own
+    # stream: copy in -> table -> forward -> backward -> copy out are ordered inside a layer's stream, and the
+    # three layers' streams overlap one another, so the two copy engines and the SMs work at the same time.
+    # Host result buffers are double-buffered; a step waits for the copies of the step two before it.
+    modules = [SparseConv2d(C, C).to(dev) for _ in KEEPS]
     with torch.no_grad():
-        module.weight.copy_(weight_h)
-        module.bias.copy_(bias_h)
+        for m in modules:
+            m.weight.copy_(weight_h)
+            m.bias.copy_(bias_h)
     pin = []
     for per_keep in host_sets:
         pk = []
         for it in per_keep:
             pk.append({k: (v.pin_memory() if hasattr(v, "pin_memory") else v) for k, v in it.items()})
         pin.append(pk)
-    out_h = [{"y": torch.empty(it["n"], C, dtype=torch.bfloat16).pin_memory(),
-              "gx": torch.empty(it["n"], C, dtype=torch.bfloat16).pin_memory()} for it in host_sets[0]]
-    gw_h = torch.empty(KK, C, C, dtype=torch.float32).pin_memory()
-    gb_h = torch.empty(C, dtype=torch.float32).pin_memory()
+    out_h = [[{"y": torch.empty(it["n"], C, dtype=torch.bfloat16).pin_memory(),
+               "gx": torch.empty(it["n"], C, dtype=torch.bfloat16).pin_memory(),
+               "gw": torch.empty(KK, C, C, dtype=torch.float32).pin_memory(),
+               "gb": torch.empty(C, dtype=torch.float32).pin_memory()} for it in host_sets[0]] for _ in range(2)]
     h2d = sum(it["scores"].numel() * 4 + it["x"].numel() * 2 + it["gy"].numel() * 2 for it in host_sets[0])
-    d2h = sum(2 * it["n"] * C * 2 for it in host_sets[0]) + 3 * (gw_h.numel() * 4 + gb_h.numel() * 4)
+    d2h = sum(2 * it["n"] * C * 2 for it in host_sets[0]) + 3 * (KK * C * C * 4 + C * 4)
+    layer_streams = [torch.cuda.Stream(device=dev) for _ in KEEPS]
+    landed = [[None] * len(KEEPS) for _ in range(2)]
 
     def e2e_step(si):
+        slot = si & 1
         for ki, it in enumerate(pin[si % N_SETS]):
-            scores = it["scores"].to(dev, non_blocking=True)
-            x = it["x"].to(dev, non_blocking=True).requires_grad_(True)
-            gy = it["gy"].to(dev, non_blocking=True)
-            kept, table = build_neighbor_table(scores, num_keep=it["k"], h=H, w=W, kernel_size=KS)
-            module.zero_grad(set_to_none=True)
-            with torch.autocast("cuda", dtype=torch.bfloat16):
-                y = module(x, table)
-            y.backward(gy)
-            if world > 1:
-                gw_r, gb_r = allreduce_weight_grads(module.weight.grad, module.bias.grad)
-                module.weight.grad, module.bias.grad = gw_r, gb_r
-            out_h[ki]["y"].copy_(y, non_blocking=True)
-            out_h[ki]["gx"].copy_(x.grad, non_blocking=True)
-            gw_h.copy_(module.weight.grad, non_blocking=True)
-            gb_h.copy_(module.bias.grad, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+            if landed[slot][ki] is not None:
+                landed[slot][ki].synchronize()
+            module = modules[ki]
+            with torch.cuda.stream(layer_streams[ki]):
+                scores = it["scores"].to(dev, non_blocking=True)
+                x = it["x"].to(dev, non_blocking=True).requires_grad_(True)
+                gy = it["gy"].to(dev, non_blocking=True)
+                kept, table = build_neighbor_table(scores, num_keep=it["k"], h=H, w=W, kernel_size=KS)
+                module.zero_grad(set_to_none=True)
+                with torch.autocast("cuda", dtype=torch.bfloat16):
+                    y = module(x, table, local_indices=False)   # tables of the builder hold global row numbers
+                y.backward(gy)
+                if world > 1:
+                    gw_r, gb_r = allreduce_weight_grads(module.weight.grad, module.bias.grad)
+                    module.weight.grad, module.bias.grad = gw_r, gb_r
+                o = out_h[slot][ki]
+                o["y"].copy_(y, non_blocking=True)
+                o["gx"].copy_(x.grad, non_blocking=True)
+                o["gw"].copy_(module.weight.grad, non_blocking=True)
+                o["gb"].copy_(module.bias.grad, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record()
+                landed[slot][ki] = ev
 
-    e2e_steps = max(3, min(args.steps, 50))
+    def e2e_drain():
+        cur = torch.cuda.current_stream()
+        for st in layer_streams:
+            cur.wait_stream(st)
+
+    # Host-side copies on a shared machine are noisy (other tenants' PCIe and memory traffic): the timed steps
+    # run as E2E_BLOCKS blocks of equal length, each bracketed by events after a full drain, and the median
+    # block is reported (all block times are kept on the line).
+    E2E_BLOCKS = 5
+    e2e_steps = max(3, min(args.steps, 50) // E2E_BLOCKS)
     for i in range(3):
         e2e_step(i)
+    e2e_drain()
     barrier()
     sampler.active = True
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for i in range(e2e_steps):
-        e2e_step(3 + i)
-    b.record()
-    barrier()
+    block_ms = []
+    step_no = 3
+    for _ in range(E2E_BLOCKS):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for st in layer_streams:
+            st.wait_stream(torch.cuda.current_stream())
+        for i in range(e2e_steps):
+            e2e_step(step_no)
+            step_no += 1
+        e2e_drain()          # every copy of every timed step has landed before the closing event
+        b.record()
+        barrier()
+        ms = a.elapsed_time(b)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        block_ms.append(ms)
     sampler.active = False
-    e2e_ms = a.elapsed_time(b)
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_ms = sorted(block_ms)[len(block_ms) // 2]
     e2e_value = world * tokens_step * e2e_steps / (e2e_ms * 1e-3)
     sampler.stop_flag = True
     assert ops.device_error() == 0, "a bounded wait inside a tensor-core kernel gave up"
@@ -513,7 +548,9 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": dict(workload_config(world), launch="cuda_graph" if graphs is not None else "eager"),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                    "stat": f"median of {E2E_BLOCKS} blocks of {e2e_steps} steps",
+                    "block_ms_per_step": [round(m / e2e_steps, 4) for m in block_ms]},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": roofline, "cpu_baseline": cpu, "reference_cuda": ref_cuda,
             "clocks": sampler.summary(),

@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_PKG, "libsvtad.so")
 
 OK, ERR_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA = 0, 1, 2, 3, 4
 F32, BF16, F16 = 0, 1, 2
-OP_FWD, OP_DGRAD, OP_WGRAD = 0, 1, 2
+OP_FWD, OP_DGRAD, OP_WGRAD, OP_BWD = 0, 1, 2, 3
 TABLE_OUT_OF_RANGE, TABLE_ASYMMETRIC = 1, 2
 
 c_int, c_i64, c_p, c_sz = ctypes.c_int, ctypes.c_int64, ctypes.c_void_p, ctypes.c_size_t
@@ -30,6 +30,7 @@ SIGNATURES = {
     "svtad_conv_fwd": (c_int, [c_p, c_p, c_p, c_p, c_p, c_i64, c_int, c_int, c_int, c_int, c_int, c_p, c_sz, c_p]),
     "svtad_conv_dgrad": (c_int, [c_p, c_p, c_p, c_p, c_i64, c_int, c_int, c_int, c_int, c_int, c_p, c_p, c_sz, c_p]),
     "svtad_conv_wgrad": (c_int, [c_p, c_p, c_p, c_p, c_p, c_i64, c_int, c_int, c_int, c_int, c_int, c_p, c_sz, c_p]),
+    "svtad_conv_bwd": (c_int, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i64, c_int, c_int, c_int, c_int, c_int, c_p, c_p, c_sz, c_p]),
     "svtad_static_workspace_bytes": (c_sz, []),
     "svtad_conv_wgrad_static": (c_int, [c_p, c_p, c_p, c_p, c_p, c_i64, c_int, c_int, c_int, c_int, c_int, c_p]),
     "svtad_device_error": (c_int, [ctypes.POINTER(ctypes.c_int32)]),

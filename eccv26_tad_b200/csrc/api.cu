@@ -1,6 +1,7 @@
 // C ABI of the SparseConv2D ops: argument validation, path selection, workspace layout.
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -45,6 +46,32 @@ static int check_common(const char* who, int64_t n, int cin, int cout, int kk, i
 
 static bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
+// Per device: a stream of the library's own and two events, used to run the weight gradient next to the
+// input gradient inside svtad_conv_bwd.  Created on first use, never destroyed (process lifetime).
+struct SideLane {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+    std::mutex mu;     // one fork .. join sequence at a time per device (events are shared)
+};
+static constexpr int MAX_DEVICES = 64;
+static SideLane g_lane[MAX_DEVICES];
+
+static bool overlap_backward() {
+    static const bool on = [] {
+        const char* e = getenv("SVTAD_OVERLAP_BACKWARD");
+        return !(e != nullptr && e[0] == '0');
+    }();
+    return on;
+}
+
+static int lane_ready(SideLane& l) {
+    if (l.stream != nullptr) return SVTAD_OK;
+    SV_CUDA(cudaStreamCreateWithFlags(&l.stream, cudaStreamNonBlocking));
+    SV_CUDA(cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming));
+    SV_CUDA(cudaEventCreateWithFlags(&l.join, cudaEventDisableTiming));
+    return SVTAD_OK;
+}
+
 }  // namespace svtad
 
 using namespace svtad;
@@ -72,6 +99,9 @@ extern "C" size_t svtad_workspace_bytes(int op, int64_t n, int cin, int cout, in
             size_t b = tc_supported(op, n, cin, cout, kk, dtype) ? tc_wgrad_ws_bytes(n, cin, cout, kk) : 0;
             return a > b ? a : b;
         }
+        case SVTAD_OP_BWD:   // both halves run at the same time: the two workspaces sit side by side
+            return align_up(svtad_workspace_bytes(SVTAD_OP_WGRAD, n, cin, cout, kk, dtype), 256) +
+                   svtad_workspace_bytes(SVTAD_OP_DGRAD, n, cin, cout, kk, dtype);
     }
     return 0;
 }
@@ -146,4 +176,53 @@ extern "C" int svtad_conv_wgrad(const void* gy, const void* x, const int32_t* nb
     if (forced_path() == 2)
         return set_error(SVTAD_ERR_UNSUPPORTED, "svtad_conv_wgrad: tensor-core path forced but shape/dtype unsupported");
     return simt_wgrad(gy, x, nbr, gw, gb, n, cin, cout, kk, tokens_per_batch, dtype, workspace, workspace_bytes, s);
+}
+
+extern "C" int svtad_conv_bwd(const void* gy, const void* x, const int32_t* nbr, const void* w, void* gx,
+                              void* gw, void* gb, int64_t n, int cin, int cout, int kk,
+                              int tokens_per_batch, int dtype, const int32_t* table_status,
+                              void* workspace, size_t workspace_bytes, void* stream) {
+    SV_CHECK_ARG(gx != nullptr || gw != nullptr, "svtad_conv_bwd: neither gx nor gw requested");
+    SV_CHECK_ARG(gb == nullptr || gw != nullptr, "svtad_conv_bwd: gb needs gw");
+    if (gw == nullptr)
+        return svtad_conv_dgrad(gy, nbr, w, gx, n, cin, cout, kk, tokens_per_batch, dtype, table_status,
+                                workspace, workspace_bytes, stream);
+    if (gx == nullptr)
+        return svtad_conv_wgrad(gy, x, nbr, gw, gb, n, cin, cout, kk, tokens_per_batch, dtype, workspace,
+                                workspace_bytes, stream);
+    // workspace = [weight-gradient part | input-gradient part (scatter form, only with a status word)]
+    const size_t w_part = align_up(svtad_workspace_bytes(SVTAD_OP_WGRAD, n, cin, cout, kk, dtype), 256);
+    const size_t d_part = table_status != nullptr ? svtad_workspace_bytes(SVTAD_OP_DGRAD, n, cin, cout, kk, dtype) : 0;
+    if (n > 0 && (workspace == nullptr || workspace_bytes < w_part + d_part))
+        return set_error(SVTAD_ERR_WORKSPACE, "svtad_conv_bwd: workspace %zu < %zu bytes", workspace_bytes,
+                         w_part + d_part);
+    void* ws_d = d_part ? static_cast<char*>(workspace) + w_part : nullptr;
+    cudaStream_t s = (cudaStream_t)stream;
+    int dev = 0;
+    SV_CUDA(cudaGetDevice(&dev));
+    if (!overlap_backward() || n == 0 || dev >= MAX_DEVICES) {
+        int rc = svtad_conv_wgrad(gy, x, nbr, gw, gb, n, cin, cout, kk, tokens_per_batch, dtype, workspace, w_part, s);
+        if (rc) return rc;
+        return svtad_conv_dgrad(gy, nbr, w, gx, n, cin, cout, kk, tokens_per_batch, dtype, table_status, ws_d, d_part, s);
+    }
+    SideLane& lane = g_lane[dev];
+    std::lock_guard<std::mutex> hold(lane.mu);
+    int rc = lane_ready(lane);
+    if (rc) return rc;
+    // fork: the side stream starts where the caller's stream stands
+    SV_CUDA(cudaEventRecord(lane.fork, s));
+    SV_CUDA(cudaStreamWaitEvent(lane.stream, lane.fork, 0));
+    int rc_w = svtad_conv_wgrad(gy, x, nbr, gw, gb, n, cin, cout, kk, tokens_per_batch, dtype, workspace, w_part,
+                                lane.stream);
+    int rc_d = svtad_conv_dgrad(gy, nbr, w, gx, n, cin, cout, kk, tokens_per_batch, dtype, table_status, ws_d,
+                                d_part, s);
+    // join, also after an error: whatever was launched on the side stream is ordered before the caller's next work
+    cudaError_t e1 = cudaEventRecord(lane.join, lane.stream);
+    cudaError_t e2 = cudaStreamWaitEvent(s, lane.join, 0);
+    if (rc_w) return rc_w;
+    if (rc_d) return rc_d;
+    if (e1 != cudaSuccess || e2 != cudaSuccess)
+        return set_error(SVTAD_ERR_CUDA, "svtad_conv_bwd: joining the side stream failed: %s",
+                         cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+    return SVTAD_OK;
 }

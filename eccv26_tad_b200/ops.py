@@ -11,8 +11,40 @@ from . import _lib
 _DTYPES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
 
 
+# Cheap equivalents of ``torch.cuda.current_stream().cuda_stream`` and ``torch.cuda.device(...)``: the
+# public helpers cost tens of microseconds per call on the host, as much as the kernels they precede.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_get_device = getattr(torch._C, "_cuda_getDevice", None)
+_exchange = getattr(torch.cuda, "_maybe_exchange_device", None)
+
+
 def _stream():
+    """Raw handle of the current stream of the current device."""
+    if _raw_stream is not None and _get_device is not None:
+        return _raw_stream(_get_device())
     return torch.cuda.current_stream().cuda_stream
+
+
+class _on:
+    """``with _on(tensor.device):`` makes that device current for the calls inside."""
+    __slots__ = ("idx", "prev", "ctx")
+
+    def __init__(self, device):
+        self.idx = device.index
+        self.ctx = None
+
+    def __enter__(self):
+        if _exchange is None or self.idx is None:
+            self.ctx = torch.cuda.device(self.idx)
+            self.ctx.__enter__()
+        else:
+            self.prev = _exchange(self.idx)
+
+    def __exit__(self, *exc):
+        if self.ctx is not None:
+            return self.ctx.__exit__(*exc)
+        _exchange(self.prev)
+        return False
 
 
 def _dtype_code(t):
@@ -65,7 +97,7 @@ def _workspace(op, n, cin, cout, kk, code, device):
 # ----------------------------------------------------------------------------- table
 def table_init(B, T, h, w, ksize=3, device="cuda"):
     out = torch.empty((B, T * h * w, ksize * ksize), dtype=torch.int32, device=device)
-    with torch.cuda.device(out.device):
+    with _on(out.device):
         _lib.check(_lib.load().svtad_table_init(B, T, h, w, ksize, _ptr(out), _stream()))
     return out
 
@@ -79,7 +111,7 @@ def table_build(scores, k_keep, h, w, ksize=3):
     n_seg, seg_len = scores.shape
     kept = torch.empty((n_seg, k_keep), dtype=torch.int32, device=scores.device)
     table = torch.empty((n_seg * k_keep, ksize * ksize), dtype=torch.int32, device=scores.device)
-    with torch.cuda.device(scores.device):
+    with _on(scores.device):
         _lib.check(_lib.load().svtad_table_build(_ptr(scores), n_seg, seg_len, k_keep, h, w, ksize,
                                                  _ptr(kept), _ptr(table), _stream()))
     return kept, table
@@ -93,7 +125,7 @@ def topk_select(scores, k_keep):
     scores = scores.contiguous()
     B, L = scores.shape
     idx = torch.empty((B, k_keep), dtype=torch.int64, device=scores.device)
-    with torch.cuda.device(scores.device):
+    with _on(scores.device):
         _lib.check(_lib.load().svtad_topk_select(_ptr(scores), B, L, k_keep, _ptr(idx), _stream()))
     return idx
 
@@ -108,7 +140,7 @@ def table_remap(table, idx, scratch=None):
     if scratch is None or scratch.numel() < B * n_prev:
         scratch = torch.empty(B * n_prev, dtype=torch.int32, device=table.device)
     out = torch.empty((B, n_new, kk), dtype=torch.int32, device=table.device)
-    with torch.cuda.device(table.device):
+    with _on(table.device):
         _lib.check(_lib.load().svtad_table_remap(_ptr(table), _ptr(idx), B, n_prev, n_new, kk,
                                                  _ptr(scratch), _ptr(out), _stream()))
     return out
@@ -128,7 +160,7 @@ def table_select_remap(scores, table, k_keep):
     kept = torch.empty((B, k_keep), dtype=torch.int32, device=table.device)
     idx = torch.empty((B, k_keep), dtype=torch.int64, device=table.device)
     out = torch.empty((B, k_keep, kk), dtype=torch.int32, device=table.device)
-    with torch.cuda.device(table.device):
+    with _on(table.device):
         _lib.check(_lib.load().svtad_table_select_remap(_ptr(scores), _ptr(table), B, n_prev, k_keep, kk, _ptr(kept),
                                                         _ptr(idx), _ptr(out), _stream()))
     return idx, out
@@ -142,7 +174,7 @@ def table_check(nbr, tokens_per_batch=0, status=None):
     n = nbr.numel() // kk
     if status is None:
         status = torch.empty(1, dtype=torch.int32, device=nbr.device)
-    with torch.cuda.device(nbr.device):
+    with _on(nbr.device):
         _lib.check(_lib.load().svtad_table_check(_ptr(nbr), n, kk, tokens_per_batch, _ptr(status), _stream()))
     return status
 
@@ -162,7 +194,7 @@ def conv_fwd(x, nbr, weight, bias=None, tokens_per_batch=0):
     if bias is not None and bias.numel() != cout:
         raise ValueError(f"conv_fwd: bias has {bias.numel()} elements, expected {cout}")
     out = torch.empty((n, cout), dtype=x.dtype, device=x.device)
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         _lib.check(_lib.load().svtad_conv_fwd(_ptr(x), _ptr(nbr), _ptr(weight),
                                               _ptr(_c16(bias)) if bias is not None else None,
                                               _ptr(out), n, cin, cout, kk, tokens_per_batch, code,
@@ -183,7 +215,7 @@ def conv_dgrad(gy, nbr, weight, tokens_per_batch=0, table_status=None, assume_sy
         raise ValueError("grad_output and weight must share one dtype")
     _check_shapes("conv_dgrad", n, kk, nbr)
     gx = torch.empty((n, cin), dtype=gy.dtype, device=gy.device)
-    with torch.cuda.device(gy.device):
+    with _on(gy.device):
         if assume_symmetric:
             status, ws, ws_bytes = None, None, 0
         else:
@@ -209,12 +241,43 @@ def conv_wgrad(gy, x, nbr, kk, tokens_per_batch=0, with_bias=True):
     _check_shapes("conv_wgrad", n, kk, nbr, grad_output=(gy, cout))
     gw = torch.empty((kk, cin, cout), dtype=x.dtype, device=x.device)
     gb = torch.empty((cout,), dtype=x.dtype, device=x.device) if with_bias else None
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         ws, ws_bytes = _workspace(_lib.OP_WGRAD, n, cin, cout, kk, code, x.device)
         _lib.check(_lib.load().svtad_conv_wgrad(_ptr(gy), _ptr(x), _ptr(nbr), _ptr(gw), _ptr(gb), n, cin,
                                                 cout, kk, tokens_per_batch, code, _ptr(ws), ws_bytes,
                                                 _stream()))
     return gw, gb
+
+
+def conv_bwd(gy, x, nbr, weight, tokens_per_batch=0, table_status=None, need_x=True, need_w=True, need_b=True):
+    """Both gradients of one layer in one library call (the weight gradient runs next to the input gradient
+    on a stream of the library; for the caller everything is ordered on the current stream).
+    Returns ``(gx, gw, gb)`` with None for what was not asked for."""
+    _require_cuda(gy, x, nbr, weight)
+    code = _dtype_code(gy)
+    kk, cin, cout = weight.shape
+    gy = _c16(gy)
+    x = _c16(x)
+    weight = _c16(weight)
+    nbr = _i32_table(nbr)
+    n = gy.numel() // cout
+    if weight.dtype != gy.dtype or x.dtype != gy.dtype:
+        raise ValueError("grad_output, x and weight must share one dtype")
+    _check_shapes("conv_bwd", n, kk, nbr, x=(x, cin))
+    need_w = need_w or need_b
+    dev = gy.device
+    gx = torch.empty((n, cin), dtype=gy.dtype, device=dev) if need_x else None
+    gw = torch.empty((kk, cin, cout), dtype=gy.dtype, device=dev) if need_w else None
+    gb = torch.empty((cout,), dtype=gy.dtype, device=dev) if need_b else None
+    with _on(dev):
+        if need_x and table_status is None:
+            table_status = table_check(nbr, tokens_per_batch)
+        op = _lib.OP_BWD if (need_x and need_w) else (_lib.OP_WGRAD if need_w else _lib.OP_DGRAD)
+        ws, ws_bytes = _workspace(op, n, cin, cout, kk, code, dev)
+        _lib.check(_lib.load().svtad_conv_bwd(_ptr(gy), _ptr(x), _ptr(nbr), _ptr(weight), _ptr(gx), _ptr(gw), _ptr(gb),
+                                              n, cin, cout, kk, tokens_per_batch, code,
+                                              _ptr(table_status) if need_x else None, _ptr(ws), ws_bytes, _stream()))
+    return gx, gw, gb
 
 
 def conv_wgrad_static(gy, x, nbr, gw, gb, tokens_per_batch=0):
@@ -234,7 +297,7 @@ def conv_wgrad_static(gy, x, nbr, gw, gb, tokens_per_batch=0):
     if nbr.dtype != torch.int32 or gy.dtype != x.dtype or gw.dtype != x.dtype:
         raise ValueError("conv_wgrad_static: nbr must be int32 and gy, x, gw must share one dtype")
     n = x.numel() // cin
-    with torch.cuda.device(x.device):
+    with _on(x.device):
         _lib.check(_lib.load().svtad_conv_wgrad_static(_ptr(gy), _ptr(x), _ptr(nbr), _ptr(gw), _ptr(gb), n, cin,
                                                        cout, kk, tokens_per_batch, code, _stream()))
     return gw, gb

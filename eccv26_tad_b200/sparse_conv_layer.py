@@ -16,7 +16,6 @@ Differences, all additive:
   take the reference's scatter formulation, so results are defined for any table.
 """
 import math
-import os
 
 import torch
 import torch.nn as nn
@@ -54,15 +53,6 @@ class _PerTableCache:
 
 
 _table_cache = _PerTableCache()
-_OVERLAP_BACKWARD = os.environ.get("SVTAD_OVERLAP_BACKWARD", "1") != "0"
-_side_streams = {}
-
-
-def _side_stream(device):
-    key = torch.device(device).index
-    if key not in _side_streams:
-        _side_streams[key] = torch.cuda.Stream(device=device)
-    return _side_streams[key]
 
 
 def _status_for(nbr, tokens_per_batch):
@@ -98,39 +88,24 @@ class SparseConv2dFunction(Function):
         nbr = neighbor_indices.reshape(-1, kk)
         grad_input = grad_weight = grad_bias = None
         need_b = bias is not None and ctx.needs_input_grad[3]
-        need_w = ctx.needs_input_grad[2] or need_b
+        need_w = ctx.needs_input_grad[2]
         need_x = ctx.needs_input_grad[0]
-        # the two halves of the backward are independent: the weight gradient runs on a side stream
-        # next to the input gradient (the reference launches them one after the other, :100-117)
-        side = _side_stream(grad_output.device) if (need_w and need_x and _OVERLAP_BACKWARD) else None
-        x2 = x.reshape(-1, ctx.C_in)
-        if need_w:
-            if side is not None:
-                cur = torch.cuda.current_stream(grad_output.device)
-                side.wait_stream(cur)
-                with torch.cuda.stream(side):
-                    gw, gb = ops.conv_wgrad(grad_output, x2, nbr, kk, tpb, with_bias=need_b)
-                for t in (grad_output, x2, nbr):
-                    t.record_stream(side)
-            else:
-                gw, gb = ops.conv_wgrad(grad_output, x2, nbr, kk, tpb, with_bias=need_b)
+        if not (need_x or need_w or need_b):
+            return None, None, None, None, None, None
+        status = None
         if need_x:
             status = ctx.table_status
             if status is None:
                 status = _status_for(neighbor_indices, tpb)
-            grad_input = ops.conv_dgrad(grad_output, nbr, weight, tpb, table_status=status)
-            if x.dim() == 3:
-                grad_input = grad_input.view(x.shape)
-        if need_w:
-            if side is not None:
-                cur.wait_stream(side)
-                gw.record_stream(cur)
-                if gb is not None:
-                    gb.record_stream(cur)
-            if ctx.needs_input_grad[2]:
-                grad_weight = gw
-            if need_b:
-                grad_bias = gb
+        # one library call: the two halves of the backward are independent, so the weight gradient runs
+        # next to the input gradient (the reference launches them one after the other, :100-117)
+        grad_input, grad_weight, grad_bias = ops.conv_bwd(grad_output, x.reshape(-1, ctx.C_in), nbr, weight, tpb,
+                                                          table_status=status, need_x=need_x, need_w=need_w,
+                                                          need_b=need_b)
+        if grad_input is not None and x.dim() == 3:
+            grad_input = grad_input.view(x.shape)
+        if not need_w:
+            grad_weight = None
         return grad_input, None, grad_weight, grad_bias, None, None
 
 

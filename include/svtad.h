@@ -45,6 +45,7 @@ extern "C" {
 #define SVTAD_OP_FWD 0
 #define SVTAD_OP_DGRAD 1
 #define SVTAD_OP_WGRAD 2
+#define SVTAD_OP_BWD 3   /* svtad_conv_bwd: both gradients in one call */
 
 /* Bits of the device status word written by svtad_table_check(). */
 #define SVTAD_TABLE_OUT_OF_RANGE 1
@@ -145,6 +146,19 @@ int svtad_conv_dgrad(const void* gy, const int32_t* nbr, const void* w, void* gx
 int svtad_conv_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw, void* gb,
                      int64_t n, int cin, int cout, int kk, int tokens_per_batch, int dtype,
                      void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * The whole backward of one layer in one call: gx as svtad_conv_dgrad, gw / gb as svtad_conv_wgrad
+ * (any of gx, gw may be NULL; gb needs gw).  When both are asked for, the weight gradient runs on a
+ * stream owned by the library next to the input gradient on `stream`, forked and joined with events, so
+ * for the caller everything is ordered on `stream`; SVTAD_OVERLAP_BACKWARD=0 keeps both on `stream`.
+ * Workspace: svtad_workspace_bytes(SVTAD_OP_BWD, ...), 256-byte aligned.
+ * Replaces the backward of SparseConv2dFunction, sparse_conv_layer.py:92-123 (bwd_in, then bwd_w, then
+ * the bias sum, one after the other).  The first call on a device creates the stream and two events.
+ */
+int svtad_conv_bwd(const void* gy, const void* x, const int32_t* nbr, const void* w, void* gx, void* gw,
+                   void* gb, int64_t n, int cin, int cout, int kk, int tokens_per_batch, int dtype,
+                   const int32_t* table_status, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
  * svtad_conv_wgrad for callers that cannot allocate device memory (no counterpart in the reference).

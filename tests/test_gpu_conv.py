@@ -254,6 +254,50 @@ def test_tensor_core_pipeline_is_race_free(monkeypatch):
     assert oconv.rel_err(f32np(first[0]), oconv.fwd(f32np(x), table.numpy(), f32np(w), f32np(b))) < 2e-2
 
 
+@pytest.mark.parametrize("dtype,C,kind", [(torch.bfloat16, 192, "geometric"), (torch.float32, 32, "geometric"),
+                                          (torch.bfloat16, 128, "arbitrary")])
+def test_one_call_backward_equals_the_two_halves(dtype, C, kind, monkeypatch):
+    """svtad_conv_bwd (weight gradient on the library's side stream) gives bit-identical results to
+    svtad_conv_dgrad + svtad_conv_wgrad, for every subset of requested gradients, repeatedly."""
+    ops = _ops()
+    if kind == "geometric":
+        _, _, table = make_table(2, 12, 14, 14, 0.3, 3, 33)
+    else:
+        rng = np.random.default_rng(33)
+        table = torch.from_numpy(rng.integers(-1, 700, size=(700, 9)).astype(np.int32))
+    n = table.shape[0]
+    x, w, b, gy = make_conv_inputs(n, C, C, 3, dtype, 33)
+    tc, xc, wc, gc = (t.cuda() for t in (table, x, w, gy))
+    gx0 = ops.conv_dgrad(gc, tc, wc)
+    gw0, gb0 = ops.conv_wgrad(gc, xc, tc, 9)
+
+    def same_gx(a):
+        if kind == "geometric":
+            return torch.equal(a, gx0)
+        # arbitrary tables take the scatter form: fp32 atomics, summation order differs from run to run
+        return oconv.rel_err(f32np(a), f32np(gx0)) < 1e-2
+
+    for _ in range(3):
+        gx, gw, gb = ops.conv_bwd(gc, xc, tc, wc)
+        assert same_gx(gx) and torch.equal(gw, gw0) and torch.equal(gb, gb0)
+    gx, gw, gb = ops.conv_bwd(gc, xc, tc, wc, need_w=False, need_b=False)
+    assert gw is None and gb is None and same_gx(gx)
+    gx, gw, gb = ops.conv_bwd(gc, xc, tc, wc, need_x=False)
+    assert gx is None and torch.equal(gw, gw0) and torch.equal(gb, gb0)
+    gx, gw, gb = ops.conv_bwd(gc, xc, tc, wc, need_b=False)
+    assert gb is None and same_gx(gx) and torch.equal(gw, gw0)
+    # the caller's stream alone orders the results: consume them at once on a non-default stream
+    st = torch.cuda.Stream()
+    st.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(st):
+        gx, gw, gb = ops.conv_bwd(gc, xc, tc, wc)
+        sums = torch.stack([gx.float().sum(), gw.float().sum(), gb.float().sum()])
+    st.synchronize()
+    ref = torch.stack([gx0.float().sum(), gw0.float().sum(), gb0.float().sum()])
+    assert torch.equal(sums[1:], ref[1:])
+    assert torch.equal(sums[:1], ref[:1]) if kind == "geometric" else abs(float(sums[0] - ref[0])) <= 1e-2 * float(gx0.float().abs().sum())
+
+
 def test_determinism_of_backward():
     _, _, table = make_table(2, 20, 14, 14, 0.3, 3, 8)
     n = table.shape[0]
