@@ -34,7 +34,9 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
                                           int lane) {
     int ok = 1;
     if (lane == 0) ok = mbar_wait(bar, parity, s_abort, err, code) ? 1 : 0;
-    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    __syncwarp();
+    return ok != 0;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -58,7 +60,9 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     TmaTail* tail = reinterpret_cast<TmaTail*>(smem + (size_t)nstage * STAGE_BYTES);
-    int* s_tab = reinterpret_cast<int*>(tail + 1);                 // [2][TILE_M * kk] table rows of a tile
+    // [TILE_M * kk] raw table rows of the next tile (landing zone of the prefetch), then [kk][4][32] the
+    // current tile's final row numbers in the order the producer lanes read them (16-byte loads)
+    int* s_tab = reinterpret_cast<int*>(tail + 1);
     volatile int* s_abort = &tail->abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -85,13 +89,13 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
         fence_mbar_init();
         tma_prefetch_map(&map_w);
     }
-    // raw table rows of a tile -> s_tab[buf], by the producer threads, one tile ahead
-    auto load_table = [&](int tile, int buf) {
+    // raw table rows of a tile -> s_tab, by the producer threads, one tile ahead
+    auto load_table = [&](int tile) {
         const long row0 = (long)(tile / n_blks) * TILE_M;
         const long rows = (n - row0) < TILE_M ? (n - row0) : TILE_M;
         const int valid_bytes = (int)rows * kk * 4;
         const char* src = reinterpret_cast<const char*>(nbr + row0 * kk);
-        const uint32_t dst = smem_u32(s_tab + buf * tab_ints);
+        const uint32_t dst = smem_u32(s_tab);
         for (int c = tid; c * 16 < tab_ints * 4; c += A_THREADS) {
             int left = valid_bytes - c * 16;
             uint32_t nb = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
@@ -100,7 +104,7 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
         cp_async_commit();
     };
     // the first tile's rows start their trip while the barriers and the tensor memory are set up
-    if (warp < A_WARPS && (int)blockIdx.x < tiles_total) load_table(blockIdx.x, 0);
+    if (warp < A_WARPS && (int)blockIdx.x < tiles_total) load_table(blockIdx.x);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -112,23 +116,24 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
         bool alive = true;
         int local = 0;
         for (int tile = blockIdx.x; tile < tiles_total; tile += gridDim.x, ++local) {
-            const int buf = local & 1;
             const long row0 = (long)(tile / n_blks) * TILE_M;
             const int n0 = (tile % n_blks) * BN;
-            int* tab = s_tab + buf * tab_ints;
-            // this tile's table rows have landed (only table copies are ever committed to a group)
+            int* xf = s_tab + tab_ints;
+            // this tile's table rows have landed (only table copies are ever committed to a group); the first
+            // barrier also says that every producer warp is done reading the previous tile's row numbers
             cp_async_wait<0>();
             named_bar_sync(1, A_THREADS);
-            // entries become final row numbers: batch offset folded in, -1 for anything that reads as zero
-            for (int e = tid; e < tab_ints; e += A_THREADS) {
-                int r = e / kk;
+            // entries become final row numbers: batch offset folded in, -1 for anything that reads as zero;
+            // stored as [tap][row & 3][row >> 2], the order in which a lane group walks a stage's rows
+            for (int d = tid; d < tab_ints; d += A_THREADS) {
+                const int k = d >> 7, r = ((d & 31) << 2) | ((d >> 5) & 3);
                 long i = row0 + r;
-                int raw = tab[e];
+                int raw = s_tab[r * kk + k];
                 long jj = (long)raw + (tpb > 0 ? (i / tpb) * (long)tpb : 0);
-                tab[e] = (i < n && raw >= 0 && jj < n) ? (int)jj : -1;
+                xf[d] = (i < n && raw >= 0 && jj < n) ? (int)jj : -1;
             }
             named_bar_sync(1, A_THREADS);
-            if (tile + (int)gridDim.x < tiles_total) load_table(tile + gridDim.x, buf ^ 1);
+            if (tile + (int)gridDim.x < tiles_total) load_table(tile + gridDim.x);
             if (!alive) continue;   // keep taking part in the barriers above
             const int it0 = local * stages_per_tile;
             // every tile walks the (tap, channel chunk) steps from its own starting point, so that CTAs
@@ -161,11 +166,15 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                 }
                 // A: 128 rows x 8 chunks of 16 B; 8 consecutive lanes cover one row's 128 B
                 const uint16_t* abase = a + c0 + sub * 8;
-                const int* trow = tab + rg * kk + k;
-                // all row numbers first, then the copies back to back
+                // all row numbers first (eight 16-byte loads, the same for the 8 lanes of a row group), then
+                // the copies back to back
+                const int4* trow = reinterpret_cast<const int4*>(xf + (k << 7) + (rg << 5));
                 int jrow[32];
 #pragma unroll
-                for (int itr = 0; itr < 32; ++itr) jrow[itr] = trow[itr * 4 * kk];
+                for (int q4 = 0; q4 < 8; ++q4) {
+                    const int4 v = trow[q4];
+                    jrow[4 * q4] = v.x; jrow[4 * q4 + 1] = v.y; jrow[4 * q4 + 2] = v.z; jrow[4 * q4 + 3] = v.w;
+                }
 #pragma unroll
                 for (int itr = 0; itr < 32; ++itr) {
                     const int j = jrow[itr];
@@ -234,7 +243,7 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
             for (int t = et; t < BN; t += 128)
                 sb[t] = (!DGRAD && bias != nullptr) ? widen(__ldg(bias + n0 + t), fp16 != 0) : 0.f;
             named_bar_sync(2, 128);
-            if (!mbar_wait(smem_u32(&tail->accum_full[buf]), (local >> 1) & 1, s_abort, err, 44)) break;
+            if (!warp_wait(smem_u32(&tail->accum_full[buf]), (local >> 1) & 1, s_abort, err, 44, lane)) break;
             tc_fence_after();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
             uint16_t* orow = out + row * cn + n0;
