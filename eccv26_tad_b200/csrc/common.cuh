@@ -79,6 +79,9 @@ int tc_read_error(int32_t* code_out);
                        cudaStream_t s);
 SV_DECLARE_TC_FAMILY(hybrid)
 SV_DECLARE_TC_FAMILY(gather4)
+// forward / dgrad on CTA pairs (conv_tc_pair.cu)
+int pair_fwd(const ConvArgs& p, cudaStream_t s);
+int pair_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s);
 
 #ifdef __CUDACC__
 // ---- device helpers ----

@@ -81,6 +81,11 @@ static EncodeTiledFn encode_fn() {
 }
 
 int tc_make_map(CUtensorMap* map, int rank, const void* base, const uint64_t* dims, const uint32_t* box, int fp16) {
+    return tc_make_map_sw(map, rank, base, dims, box, fp16, 128);
+}
+
+int tc_make_map_sw(CUtensorMap* map, int rank, const void* base, const uint64_t* dims, const uint32_t* box, int fp16,
+                   int swizzle_bytes) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return set_error(SVTAD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     // the driver call needs this thread to hold the device's context (autograd worker threads may not yet)
@@ -102,7 +107,8 @@ int tc_make_map(CUtensorMap* map, int rank, const void* base, const uint64_t* di
     }
     CUresult r = fn(map, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank,
                     const_cast<void*>(base), gdim, gstride, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return set_error(SVTAD_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return SVTAD_OK;
@@ -231,9 +237,19 @@ static bool use_gather4() {
     return e != nullptr && e[0] == 'g';
 }
 
-int tc_fwd(const ConvArgs& p, cudaStream_t s) { return use_gather4() ? gather4_fwd(p, s) : hybrid_fwd(p, s); }
+// SVTAD_TC_IMPL=pair: forward / dgrad on CTA pairs (tcgen05 cta_group::2)
+static bool use_pair() {
+    const char* e = getenv("SVTAD_TC_IMPL");
+    return e != nullptr && e[0] == 'p';
+}
+
+int tc_fwd(const ConvArgs& p, cudaStream_t s) {
+    if (use_pair()) return pair_fwd(p, s);
+    return use_gather4() ? gather4_fwd(p, s) : hybrid_fwd(p, s);
+}
 
 int tc_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s) {
+    if (use_pair()) return pair_dgrad(p, status, s);
     return use_gather4() ? gather4_dgrad(p, status, s) : hybrid_dgrad(p, status, s);
 }
 

@@ -224,6 +224,9 @@ int tc_num_sms();
 bool tc_rotate_enabled();   // SVTAD_TC_ROTATE=0 makes every CTA walk its K steps in the same order
 // 16-bit tensor map with 128-byte swizzle and zero fill outside the tensor; dims[0] is the contiguous one
 int tc_make_map(CUtensorMap* map, int rank, const void* base, const uint64_t* dims, const uint32_t* box, int fp16);
+// same with a 64- or 128-byte swizzle
+int tc_make_map_sw(CUtensorMap* map, int rank, const void* base, const uint64_t* dims, const uint32_t* box, int fp16,
+                   int swizzle_bytes);
 // column-block width of a forward / dgrad CTA for an output of `cn` columns and `m_tiles` row tiles
 int tc_pick_bn(int cn, long m_tiles);
 struct WgradPlan {
