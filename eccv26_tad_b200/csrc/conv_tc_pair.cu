@@ -39,7 +39,7 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
     return r;
 }
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -264,11 +264,11 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
             uint32_t ph = 0;
             for (int item = cid; item < items_total && alive; item += n_clusters, ++local) {
                 const int buf = local & 1;
-                if (!mbar_wait_cluster(smem_u32(&tail->accum_empty[buf]), ((local >> 1) & 1) ^ 1, s_abort, err, 52)) { alive = false; break; }
+                if (!mbar_wait(smem_u32(&tail->accum_empty[buf]), ((local >> 1) & 1) ^ 1, s_abort, err, 52)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int st = 0; st < stages_per_tile; ++st) {
-                    if (!mbar_wait_cluster(smem_u32(&tail->full[s]), ph, s_abort, err, 53)) { alive = false; break; }
+                    if (!mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 53)) { alive = false; break; }
                     fence_proxy_async();
                     tc_fence_after();
                     const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
