@@ -28,6 +28,7 @@ def _no_forced_path(monkeypatch):
     monkeypatch.delenv("SVTAD_FORCE_PATH", raising=False)
     monkeypatch.delenv("SVTAD_TC_BN", raising=False)
     monkeypatch.delenv("SVTAD_TC_WGRAD_CLUSTER", raising=False)
+    monkeypatch.delenv("SVTAD_TC_IMPL", raising=False)
     yield
     assert _ops().device_error() == 0, "a bounded wait inside a tensor-core kernel gave up"
 
@@ -96,6 +97,52 @@ def test_tc_column_block_variants(bn, monkeypatch):
     x, w, b, gy = make_conv_inputs(n, 192, 192, 3, torch.bfloat16, 99, bias="random")
     outs = _run_all(table, x, w, b, gy)
     _check_all(table, x, w, b, gy, outs, 2e-2)
+
+
+@pytest.mark.parametrize("C,ks,dtype,shape", [
+    (192, 3, torch.bfloat16, (2, 20, 0.3)),      # 19 row tiles: odd, the last pair's second CTA has no rows
+    (192, 3, torch.float16, (1, 3, 0.55)),
+    (64, 3, torch.bfloat16, (1, 9, 0.3)),
+    (128, 3, torch.bfloat16, (1, 7, 1.0)),
+    (256, 5, torch.bfloat16, (1, 6, 0.3)),
+    (1024, 3, torch.bfloat16, (1, 6, 0.3)),      # several column blocks per row-tile pair
+    (192, 3, torch.bfloat16, (2, 80, 0.55)),     # 135 tiles on 74 CTA pairs: persistent loop, two accumulators
+])
+def test_cta_pair_kernels(C, ks, dtype, shape, monkeypatch):
+    """Forward / dgrad on CTA pairs (tcgen05 cta_group::2, the default for large inputs) against the oracle."""
+    monkeypatch.setenv("SVTAD_TC_IMPL", "pair")
+    B, T, keep = shape
+    _, _, table = make_table(B, T, 14, 14, keep, ks, 77)
+    n = table.shape[0]
+    x, w, b, gy = make_conv_inputs(n, C, C, ks, dtype, 77, bias="random")
+    outs = _run_all(table, x, w, b, gy)
+    _check_all(table, x, w, b, gy, outs, 2e-2)
+    monkeypatch.setenv("SVTAD_TC_IMPL", "hybrid")
+    ref = _run_all(table, x, w, b, gy)
+    for u, v in zip(outs[:2], ref[:2]):
+        assert oconv.rel_err(f32np(u), f32np(v)) < 8e-3      # same products, fp32 accumulate, one rounding
+
+
+def test_cta_pair_kernels_ragged_rows_and_batch_local_indices(monkeypatch):
+    monkeypatch.setenv("SVTAD_TC_IMPL", "pair")
+    for n in (1, 129, 1000):
+        table = -np.ones((n, 9), dtype=np.int32)
+        table[:, 4] = np.arange(n)
+        table[1:, 3] = np.arange(n - 1)
+        table[:-1, 5] = np.arange(1, n)
+        table = torch.from_numpy(table)
+        x, w, b, gy = make_conv_inputs(n, 192, 64, 3, torch.bfloat16, n, bias="random")
+        outs = _run_all(table, x, w, b, gy)
+        _check_all(table, x, w, b, gy, outs, 2e-2)
+    # indices local to each batch row
+    _, _, glob = make_table(3, 4, 14, 14, 0.3, 3, 9)
+    n = glob.shape[0]
+    tpb = n // 3
+    local = glob.clone()
+    local[local >= 0] %= tpb
+    x, w, b, gy = make_conv_inputs(n, 128, 128, 3, torch.bfloat16, 9, bias="random")
+    outs = _run_all(local, x, w, b, gy, tpb=tpb)
+    _check_all(local, x, w, b, gy, outs, 2e-2, tpb=tpb)
 
 
 def test_wgrad_cluster_reduction_variant(monkeypatch):
