@@ -262,17 +262,24 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
             bool alive = true;
             int local = 0, s = 0;
             uint32_t ph = 0;
+            bool ready = false;   // result of probing this step's barrier while the previous step's MMAs were issued
+            // distance from one of this CTA's shared-memory addresses to the same location in the odd CTA
+            const uint32_t to_peer = map_to_cta(stage_base, 1) - stage_base;
             for (int item = cid; item < items_total && alive; item += n_clusters, ++local) {
                 const int buf = local & 1;
                 if (!mbar_wait(smem_u32(&tail->accum_empty[buf]), ((local >> 1) & 1) ^ 1, s_abort, err, 52)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int st = 0; st < stages_per_tile; ++st) {
-                    if (!mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 53)) { alive = false; break; }
+                    if (!ready && !mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 53)) { alive = false; break; }
                     fence_proxy_async();
                     tc_fence_after();
                     const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
                     const uint32_t b_tile = a_tile + A_TILE_BYTES;
+                    int sn = s + 1;
+                    uint32_t phn = ph;
+                    if (sn == nstage) { sn = 0; phn ^= 1u; }
+                    ready = mbar_test_wait(smem_u32(&tail->full[sn]), phn);
 #pragma unroll
                     for (int ks = 0; ks < STAGE_K / 16; ++ks) {
                         uint64_t ad = make_smem_desc(a_tile + ks * 32, 0, 1024);
@@ -283,13 +290,14 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
                     }
                     const uint32_t e_local = smem_u32(&tail->empty[s]);
                     umma_pair_commit(e_local);
-                    umma_pair_commit(map_to_cta(e_local, 1));
-                    if (++s == nstage) { s = 0; ph ^= 1u; }
+                    umma_pair_commit(e_local + to_peer);
+                    s = sn;
+                    ph = phn;
                 }
                 if (alive) {
                     const uint32_t f_local = smem_u32(&tail->accum_full[buf]);
                     umma_pair_commit(f_local);
-                    umma_pair_commit(map_to_cta(f_local, 1));
+                    umma_pair_commit(f_local + to_peer);
                 }
             }
         } else if (lane == 0) {
