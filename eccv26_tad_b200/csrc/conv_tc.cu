@@ -238,14 +238,14 @@ static bool use_gather4() {
 }
 
 // Forward / dgrad on CTA pairs (tcgen05 cta_group::2) or on single CTAs.  Measured on B200 at C = 192: pairs win
-// once the row tiles fill the SMs at least twice (869-890 vs 820-850 TFLOP/s at 226 560 rows); below that one
-// CTA per (row tile, column block) starts sooner and uses narrower column blocks to fill the machine.
+// once there are more row tiles than SMs (918-941 vs 820-850 TFLOP/s at 226 560 rows); below that one CTA
+// per (row tile, column block) starts sooner and uses narrower column blocks to fill the machine.
 // SVTAD_TC_IMPL=pair / hybrid / gather4 overrides the choice.
 static bool use_pair(int64_t n) {
     const char* e = getenv("SVTAD_TC_IMPL");
     if (e != nullptr && *e) return e[0] == 'p';
     const long m_tiles = (n + TILE_M - 1) / TILE_M;
-    return m_tiles >= 2l * tc_num_sms();
+    return m_tiles > (long)tc_num_sms();
 }
 
 int tc_fwd(const ConvArgs& p, cudaStream_t s) {

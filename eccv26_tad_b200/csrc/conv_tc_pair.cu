@@ -111,8 +111,8 @@ __device__ __forceinline__ bool warp_wait_pair(uint32_t bar, uint32_t parity, vo
     return ok != 0;
 }
 
-struct alignas(16) PairTail {
-    uint64_t full[8];          // even CTA: 32 copy arrivals + TMA + the odd CTA's relay; odd CTA: 32 + TMA
+struct alignas(16) PairTail {   // barriers are per round of two 64-deep buffers
+    uint64_t full[8];          // per half 32 copy arrivals + TMA; the even CTA's also counts the odd CTA's relay
     uint64_t empty[8];         // one arrival: the even CTA's tcgen05.commit
     uint64_t accum_full[2];    // one arrival: the even CTA's tcgen05.commit
     uint64_t accum_empty[2];   // even CTA only: one arrival per epilogue warp of both CTAs
@@ -148,6 +148,11 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
     const int items_total = m_pairs * n_blks;
     const int kchunks = cred / STAGE_K;
     const int stages_per_tile = kk * kchunks;
+    // Two 64-deep buffers form one barrier round (a 128-deep K step): the MMA thread's per-round work (wait,
+    // fences, commits) is spent once per eight instructions instead of once per four.  A tile with an odd
+    // number of 64-deep steps gets an empty last half: its owner only arrives on the barrier.
+    const int sp_pad = (stages_per_tile + 1) & ~1;
+    const int nbig = nstage >> 1;             // nstage (number of 64-deep buffers) is even
     const int tab_ints = TILE_M * kk;
     float* s_bias = reinterpret_cast<float*>(s_tab + 2 * tab_ints);   // [2][256]
 
@@ -156,9 +161,9 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
         tmem_relinquish_pair();
     }
     if (tid == 0) {
-        for (int s = 0; s < nstage; ++s) {
-            mbar_init(smem_u32(&tail->full[s]), rank == 0 ? 34 : 33);
-            mbar_init(smem_u32(&tail->empty[s]), 1);
+        for (int b = 0; b < nbig; ++b) {
+            mbar_init(smem_u32(&tail->full[b]), rank == 0 ? 67 : 66);   // two halves x (32 copies + TMA), + the relay
+            mbar_init(smem_u32(&tail->empty[b]), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&tail->accum_full[b]), 1);
@@ -210,44 +215,50 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
             named_bar_sync(1, PR_A_THREADS);
             if (item + n_clusters < items_total) load_table(item + n_clusters);
             if (!alive) continue;
-            const int it0 = local * stages_per_tile;
+            const int it0 = local * sp_pad;
             int st = (warp - it0) & (PR_A_WARPS - 1);
-            int s = (it0 + st) % nstage;
+            int s = (it0 + st) % nstage;                         // 64-deep buffer; its barrier round is s >> 1
             uint32_t ph = (((it0 + st) / nstage) & 1) ^ 1;
             int k = st / kchunks, kc = st - k * kchunks;
-            for (; st < stages_per_tile; st += PR_A_WARPS) {
-                if (!warp_wait_pair(smem_u32(&tail->empty[s]), ph, s_abort, err, 51, lane)) { alive = false; break; }
+            for (; st < sp_pad; st += PR_A_WARPS) {
+                if (!warp_wait_pair(smem_u32(&tail->empty[s >> 1]), ph, s_abort, err, 51, lane)) { alive = false; break; }
                 const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
-                const uint32_t bar = smem_u32(&tail->full[s]);
-                const int c0 = kc * STAGE_K;
-                if (lane == 0) {
-                    const uint32_t b_tile = a_tile + A_TILE_BYTES;
-                    const int wtap = DGRAD ? (kk - 1 - k) : k;
-                    mbar_expect_tx(bar, B_BYTES);
-                    if (!DGRAD) {
+                const uint32_t bar = smem_u32(&tail->full[s >> 1]);
+                if (st >= stages_per_tile) {
+                    // the empty half of the tile's last round: same number of arrivals, nothing to copy
+                    mbar_arrive(bar);
+                    if (lane == 0) mbar_arrive(bar);
+                } else {
+                    const int c0 = kc * STAGE_K;
+                    if (lane == 0) {
+                        const uint32_t b_tile = a_tile + A_TILE_BYTES;
+                        const int wtap = DGRAD ? (kk - 1 - k) : k;
+                        mbar_expect_tx(bar, B_BYTES);
+                        if (!DGRAD) {
 #pragma unroll
-                        for (int b = 0; b < HALF / 32; ++b)
-                            tma_load_3d(b_tile + b * 4096, &map_w, n0 + b * 32, c0, wtap, bar);
-                    } else {
-                        tma_load_3d(b_tile, &map_w, c0, n0, wtap, bar);
+                            for (int b = 0; b < HALF / 32; ++b)
+                                tma_load_3d(b_tile + b * 4096, &map_w, n0 + b * 32, c0, wtap, bar);
+                        } else {
+                            tma_load_3d(b_tile, &map_w, c0, n0, wtap, bar);
+                        }
                     }
-                }
-                const uint16_t* abase = a + c0 + sub * 8;
-                const int4* trow = reinterpret_cast<const int4*>(xf + (k << 7) + (rg << 5));
-                int jrow[32];
+                    const uint16_t* abase = a + c0 + sub * 8;
+                    const int4* trow = reinterpret_cast<const int4*>(xf + (k << 7) + (rg << 5));
+                    int jrow[32];
 #pragma unroll
-                for (int q4 = 0; q4 < 8; ++q4) {
-                    const int4 v = trow[q4];
-                    jrow[4 * q4] = v.x; jrow[4 * q4 + 1] = v.y; jrow[4 * q4 + 2] = v.z; jrow[4 * q4 + 3] = v.w;
-                }
+                    for (int q4 = 0; q4 < 8; ++q4) {
+                        const int4 v = trow[q4];
+                        jrow[4 * q4] = v.x; jrow[4 * q4 + 1] = v.y; jrow[4 * q4 + 2] = v.z; jrow[4 * q4 + 3] = v.w;
+                    }
 #pragma unroll
-                for (int itr = 0; itr < 32; ++itr) {
-                    const int j = jrow[itr];
-                    const int r7 = ((itr & 1) << 2) | rg;
-                    const uint32_t dst = a_tile + (itr * 4 + rg) * 128 + ((sub ^ r7) << 4);
-                    cp_async16(dst, abase + (long)(j < 0 ? 0 : j) * cred, j < 0 ? 0u : 16u);
+                    for (int itr = 0; itr < 32; ++itr) {
+                        const int j = jrow[itr];
+                        const int r7 = ((itr & 1) << 2) | rg;
+                        const uint32_t dst = a_tile + (itr * 4 + rg) * 128 + ((sub ^ r7) << 4);
+                        cp_async16(dst, abase + (long)(j < 0 ? 0 : j) * cred, j < 0 ? 0u : 16u);
+                    }
+                    cp_async_arrive_noinc(bar);
                 }
-                cp_async_arrive_noinc(bar);
                 s += PR_A_WARPS;
                 while (s >= nstage) { s -= nstage; ph ^= 1u; }
                 kc += PR_A_WARPS;
@@ -270,23 +281,27 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
                 if (!mbar_wait(smem_u32(&tail->accum_empty[buf]), ((local >> 1) & 1) ^ 1, s_abort, err, 52)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int st = 0; st < stages_per_tile; ++st) {
+                for (int st = 0; st < sp_pad; st += 2) {
                     if (!ready && !mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 53)) { alive = false; break; }
                     fence_proxy_async();
                     tc_fence_after();
-                    const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
-                    const uint32_t b_tile = a_tile + A_TILE_BYTES;
+                    const uint32_t a_tile = stage_base + (uint32_t)(2 * s) * STAGE_BYTES;
                     int sn = s + 1;
                     uint32_t phn = ph;
-                    if (sn == nstage) { sn = 0; phn ^= 1u; }
+                    if (sn == nbig) { sn = 0; phn ^= 1u; }
                     ready = mbar_test_wait(smem_u32(&tail->full[sn]), phn);
+                    const int halves = (st + 1 < stages_per_tile) ? 2 : 1;
+                    for (int h = 0; h < halves; ++h) {
+                        const uint32_t a_h = a_tile + (uint32_t)h * STAGE_BYTES;
+                        const uint32_t b_h = a_h + A_TILE_BYTES;
 #pragma unroll
-                    for (int ks = 0; ks < STAGE_K / 16; ++ks) {
-                        uint64_t ad = make_smem_desc(a_tile + ks * 32, 0, 1024);
-                        // forward: 16 K rows of 64 B per step, 8-row groups 512 B apart, 32-column atoms 4 KB apart
-                        uint64_t bd = DGRAD ? make_smem_desc(b_tile + ks * 32, 0, 1024)
-                                            : make_smem_desc_layout(b_tile + ks * 1024, 4096, 512, 4);
-                        umma_pair_f16(d_tmem, ad, bd, idesc, (st | ks) != 0 ? 1u : 0u);
+                        for (int ks = 0; ks < STAGE_K / 16; ++ks) {
+                            uint64_t ad = make_smem_desc(a_h + ks * 32, 0, 1024);
+                            // forward: 16 K rows of 64 B per step, 8-row groups 512 B apart, 32-column atoms 4 KB apart
+                            uint64_t bd = DGRAD ? make_smem_desc(b_h + ks * 32, 0, 1024)
+                                                : make_smem_desc_layout(b_h + ks * 1024, 4096, 512, 4);
+                            umma_pair_f16(d_tmem, ad, bd, idesc, (st | h | ks) != 0 ? 1u : 0u);
+                        }
                     }
                     const uint32_t e_local = smem_u32(&tail->empty[s]);
                     umma_pair_commit(e_local);
@@ -306,11 +321,11 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
             int s = 0;
             uint32_t ph = 0;
             for (int item = cid; item < items_total && alive; item += n_clusters) {
-                for (int st = 0; st < stages_per_tile; ++st) {
+                for (int st = 0; st < sp_pad; st += 2) {
                     if (!mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 54)) { alive = false; break; }
                     fence_proxy_async();      // this CTA's cp.async writes -> the even CTA's tcgen05.mma reads
                     mbar_arrive_cluster(map_to_cta(smem_u32(&tail->full[s]), 0));
-                    if (++s == nstage) { s = 0; ph ^= 1u; }
+                    if (++s == nbig) { s = 0; ph ^= 1u; }
                 }
             }
         }
@@ -393,8 +408,9 @@ static int launch_conv_pair(const ConvArgs& p, const int32_t* status, cudaStream
     const size_t stage = A_TILE_BYTES + (size_t)HALF * 128;
     const size_t extra = sizeof(PairTail) + 2 * (size_t)TILE_M * p.kk * sizeof(int) + 2 * 256 * sizeof(float);
     int nstage = (int)((TC_SMEM_LIMIT - 1024 - extra) / stage);
-    if (nstage > 8) nstage = 8;
-    if (nstage < 2)
+    if (nstage > 16) nstage = 16;
+    nstage &= ~1;      // two 64-deep buffers per barrier round
+    if (nstage < 4)
         return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core conv (CTA pairs): not enough shared memory for BN=%d kk=%d", BN, p.kk);
     const size_t smem = 1024 + nstage * stage + extra;
     auto kern = conv_pair_kernel<BN, DGRAD>;
