@@ -42,7 +42,8 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 // ---------------------------------------------------------------------------------------------
 // forward / dgrad
 // ---------------------------------------------------------------------------------------------
-template <int BN, bool DGRAD>
+// RB = 64-deep buffers per barrier round (1 or 2).
+template <int BN, bool DGRAD, int RB>
 __global__ void __launch_bounds__(HY_THREADS, 1)
 conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __restrict__ a,
                    const int32_t* __restrict__ nbr, const uint16_t* __restrict__ bias,
@@ -70,6 +71,13 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
     const int tiles_total = m_tiles * n_blks;
     const int kchunks = cred / STAGE_K;
     const int stages_per_tile = kk * kchunks;
+    // With RB = 2, two 64-deep buffers form one barrier round (a 128-deep K step): the MMA thread's per-round
+    // work (wait, fences, commit) is spent once per eight instructions instead of once per four - worth it when
+    // at least three rounds fit in shared memory.  A tile with an odd number of 64-deep steps gets an empty last
+    // half: its owner only arrives on the barrier.
+    const int sp_pad = RB == 2 ? ((stages_per_tile + 1) & ~1) : stages_per_tile;
+    const int nbig = nstage / RB;             // nstage (number of 64-deep buffers) is a multiple of RB
+    constexpr int RSH = RB == 2 ? 1 : 0;      // buffer -> barrier round
     const int tab_ints = TILE_M * kk;
 
     if (warp == 4) {
@@ -77,9 +85,9 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
         tmem_relinquish();
     }
     if (tid == 0) {
-        for (int s = 0; s < nstage; ++s) {
-            mbar_init(smem_u32(&tail->full[s]), 33);    // 32 copy arrivals + the TMA byte-count arrival
-            mbar_init(smem_u32(&tail->empty[s]), 1);
+        for (int b = 0; b < nbig; ++b) {
+            mbar_init(smem_u32(&tail->full[b]), 33 * RB);    // per buffer: 32 copy arrivals + the TMA byte-count arrival
+            mbar_init(smem_u32(&tail->empty[b]), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&tail->accum_full[b]), 1);
@@ -135,54 +143,55 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
             named_bar_sync(1, A_THREADS);
             if (tile + (int)gridDim.x < tiles_total) load_table(tile + gridDim.x);
             if (!alive) continue;   // keep taking part in the barriers above
-            const int it0 = local * stages_per_tile;
-            // every tile walks the (tap, channel chunk) steps from its own starting point, so that CTAs
-            // running side by side pull different weight tiles out of L2 instead of the same one
-            const int rot = rotate ? (int)(((long)tile * 11) % stages_per_tile) : 0;
-            // first step of this tile that this warp owns; then every A_WARPS-th one.  Slot, phase and
+            const int it0 = local * sp_pad;
+            // first step of this tile that this warp owns; then every A_WARPS-th one.  Buffer, phase and
             // (tap, chunk) advance incrementally: no division in the loop.
             int st = (warp - it0) & (A_WARPS - 1);
-            int s = (it0 + st) % nstage;
+            int s = (it0 + st) % nstage;                         // 64-deep buffer; its barrier round is s >> 1
             uint32_t ph = (((it0 + st) / nstage) & 1) ^ 1;
-            int sr = (st + rot) % stages_per_tile;
-            int k = sr / kchunks, kc = sr - k * kchunks;
-            for (; st < stages_per_tile; st += A_WARPS) {
-                const int it = it0 + st;
-                if (!warp_wait(smem_u32(&tail->empty[s]), ph, s_abort, err, 41, lane)) { alive = false; break; }
+            int k = st / kchunks, kc = st - k * kchunks;
+            for (; st < sp_pad; st += A_WARPS) {
+                if (!warp_wait(smem_u32(&tail->empty[s >> RSH]), ph, s_abort, err, 41, lane)) { alive = false; break; }
                 const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
-                const uint32_t bar = smem_u32(&tail->full[s]);
-                const int c0 = kc * STAGE_K;
-                if (lane == 0) {
-                    const uint32_t b_tile = a_tile + A_TILE_BYTES;
-                    const int wtap = DGRAD ? (kk - 1 - k) : k;
-                    mbar_expect_tx(bar, B_TX_BYTES);
-                    if (!DGRAD) {
+                const uint32_t bar = smem_u32(&tail->full[s >> RSH]);
+                if (RB == 2 && st >= stages_per_tile) {
+                    // the empty half of the tile's last round: same number of arrivals, nothing to copy
+                    mbar_arrive(bar);
+                    if (lane == 0) mbar_arrive(bar);
+                } else {
+                    const int c0 = kc * STAGE_K;
+                    if (lane == 0) {
+                        const uint32_t b_tile = a_tile + A_TILE_BYTES;
+                        const int wtap = DGRAD ? (kk - 1 - k) : k;
+                        mbar_expect_tx(bar, B_TX_BYTES);
+                        if (!DGRAD) {
 #pragma unroll
-                        for (int b = 0; b < B_TILE_BYTES / 8192; ++b)
-                            tma_load_3d(b_tile + b * 8192, &map_w, n0 + b * 64, c0, wtap, bar);
-                    } else {
-                        tma_load_3d(b_tile, &map_w, c0, n0, wtap, bar);
+                            for (int b = 0; b < B_TILE_BYTES / 8192; ++b)
+                                tma_load_3d(b_tile + b * 8192, &map_w, n0 + b * 64, c0, wtap, bar);
+                        } else {
+                            tma_load_3d(b_tile, &map_w, c0, n0, wtap, bar);
+                        }
                     }
-                }
-                // A: 128 rows x 8 chunks of 16 B; 8 consecutive lanes cover one row's 128 B
-                const uint16_t* abase = a + c0 + sub * 8;
-                // all row numbers first (eight 16-byte loads, the same for the 8 lanes of a row group), then
-                // the copies back to back
-                const int4* trow = reinterpret_cast<const int4*>(xf + (k << 7) + (rg << 5));
-                int jrow[32];
+                    // A: 128 rows x 8 chunks of 16 B; 8 consecutive lanes cover one row's 128 B
+                    const uint16_t* abase = a + c0 + sub * 8;
+                    // all row numbers first (eight 16-byte loads, the same for the 8 lanes of a row group), then
+                    // the copies back to back
+                    const int4* trow = reinterpret_cast<const int4*>(xf + (k << 7) + (rg << 5));
+                    int jrow[32];
 #pragma unroll
-                for (int q4 = 0; q4 < 8; ++q4) {
-                    const int4 v = trow[q4];
-                    jrow[4 * q4] = v.x; jrow[4 * q4 + 1] = v.y; jrow[4 * q4 + 2] = v.z; jrow[4 * q4 + 3] = v.w;
-                }
+                    for (int q4 = 0; q4 < 8; ++q4) {
+                        const int4 v = trow[q4];
+                        jrow[4 * q4] = v.x; jrow[4 * q4 + 1] = v.y; jrow[4 * q4 + 2] = v.z; jrow[4 * q4 + 3] = v.w;
+                    }
 #pragma unroll
-                for (int itr = 0; itr < 32; ++itr) {
-                    const int j = jrow[itr];
-                    const int r7 = ((itr & 1) << 2) | rg;            // (row & 7) for row = itr * 4 + rg
-                    const uint32_t dst = a_tile + (itr * 4 + rg) * 128 + ((sub ^ r7) << 4);
-                    cp_async16(dst, abase + (long)(j < 0 ? 0 : j) * cred, j < 0 ? 0u : 16u);
+                    for (int itr = 0; itr < 32; ++itr) {
+                        const int j = jrow[itr];
+                        const int r7 = ((itr & 1) << 2) | rg;            // (row & 7) for row = itr * 4 + rg
+                        const uint32_t dst = a_tile + (itr * 4 + rg) * 128 + ((sub ^ r7) << 4);
+                        cp_async16(dst, abase + (long)(j < 0 ? 0 : j) * cred, j < 0 ? 0u : 16u);
+                    }
+                    cp_async_arrive_noinc(bar);
                 }
-                cp_async_arrive_noinc(bar);
                 s += A_WARPS;
                 while (s >= nstage) { s -= nstage; ph ^= 1u; }
                 kc += A_WARPS;
@@ -195,7 +204,7 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
         if (lane == 0) {
             const uint32_t idesc = make_idesc(fp16 ? 0 : 1, 0, DGRAD ? 0 : 1, TILE_M, BN);
             bool alive = true;
-            int it = 0, local = 0, s = 0;
+            int local = 0, s = 0;
             uint32_t ph = 0;
             bool ready = false;   // result of probing this step's barrier while the previous step's MMAs were issued
             for (int tile = blockIdx.x; tile < tiles_total && alive; tile += gridDim.x, ++local) {
@@ -203,22 +212,26 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                 if (!mbar_wait(smem_u32(&tail->accum_empty[buf]), ((local >> 1) & 1) ^ 1, s_abort, err, 42)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int st = 0; st < stages_per_tile; ++st, ++it) {
+                for (int st = 0; st < sp_pad; st += RB) {
                     if (!ready && !mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 43)) { alive = false; break; }
                     fence_proxy_async();   // cp.async (generic proxy) writes -> tcgen05.mma (async proxy) reads
                     tc_fence_after();
-                    const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
-                    const uint32_t b_tile = a_tile + A_TILE_BYTES;
+                    const uint32_t a_tile = stage_base + (uint32_t)(RB * s) * STAGE_BYTES;
                     int sn = s + 1;
                     uint32_t phn = ph;
-                    if (sn == nstage) { sn = 0; phn ^= 1u; }
+                    if (sn == nbig) { sn = 0; phn ^= 1u; }
                     ready = mbar_test_wait(smem_u32(&tail->full[sn]), phn);   // answer arrives while the MMAs issue
+                    const int halves = (RB == 2 && st + 1 < stages_per_tile) ? 2 : 1;
+                    for (int h = 0; h < halves; ++h) {
+                        const uint32_t a_h = a_tile + (uint32_t)h * STAGE_BYTES;
+                        const uint32_t b_h = a_h + A_TILE_BYTES;
 #pragma unroll
-                    for (int ks = 0; ks < STAGE_K / 16; ++ks) {
-                        uint64_t ad = make_smem_desc(a_tile + ks * 32, 0, 1024);
-                        uint64_t bd = DGRAD ? make_smem_desc(b_tile + ks * 32, 0, 1024)
-                                            : make_smem_desc(b_tile + ks * 2048, 8192, 1024);
-                        umma_f16(d_tmem, ad, bd, idesc, (st | ks) != 0 ? 1u : 0u);
+                        for (int ks = 0; ks < STAGE_K / 16; ++ks) {
+                            uint64_t ad = make_smem_desc(a_h + ks * 32, 0, 1024);
+                            uint64_t bd = DGRAD ? make_smem_desc(b_h + ks * 32, 0, 1024)
+                                                : make_smem_desc(b_h + ks * 2048, 8192, 1024);
+                            umma_f16(d_tmem, ad, bd, idesc, (st | h | ks) != 0 ? 1u : 0u);
+                        }
                     }
                     umma_commit(smem_u32(&tail->empty[s]));
                     s = sn;
@@ -588,11 +601,14 @@ static int launch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaStre
     const size_t stage = A_TILE_BYTES + b_tile_bytes_for(BN);
     const size_t extra = sizeof(TmaTail) + 2 * (size_t)TILE_M * p.kk * sizeof(int) + 2 * 256 * sizeof(float);
     int nstage = (int)((TC_SMEM_LIMIT - 1024 - extra) / stage);
-    if (nstage > 8) nstage = 8;
+    if (nstage > 16) nstage = 16;
     if (nstage < 2)
         return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core conv: not enough shared memory for BN=%d kk=%d", BN, p.kk);
+    // rounds of two buffers once three rounds fit (narrow column blocks); otherwise one buffer per round
+    const bool two = nstage >= 6;
+    if (two) nstage &= ~1;
     const size_t smem = 1024 + nstage * stage + extra;
-    auto kern = conv_hybrid_kernel<BN, DGRAD>;
+    auto kern = two ? conv_hybrid_kernel<BN, DGRAD, 2> : conv_hybrid_kernel<BN, DGRAD, 1>;
     SV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int m_tiles = (int)((p.n + TILE_M - 1) / TILE_M);
     const int n_blks = cn / BN;
@@ -600,7 +616,7 @@ static int launch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaStre
     int grid = (int)(tiles < tc_num_sms() ? tiles : tc_num_sms());
     SV_CUDA(tc_launch(kern, dim3(grid), dim3(HY_THREADS), smem, s, map_w, (const uint16_t*)p.a, p.nbr,
                       (const uint16_t*)p.bias, (uint16_t*)p.out, status, (long)p.n, cred, cn, p.kk, p.tpb, nstage, fp16,
-                      m_tiles, n_blks, tc_rotate_enabled() ? 1 : 0, tc_error_ptr()));
+                      m_tiles, n_blks, 0, tc_error_ptr()));
     return SVTAD_OK;
 }
 
