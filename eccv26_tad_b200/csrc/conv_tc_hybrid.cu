@@ -48,8 +48,7 @@ __global__ void __launch_bounds__(HY_THREADS, 1)
 conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __restrict__ a,
                    const int32_t* __restrict__ nbr, const uint16_t* __restrict__ bias,
                    uint16_t* __restrict__ out, const int32_t* __restrict__ status, long n, int cred, int cn,
-                   int kk, int tpb, int nstage, int fp16, int m_tiles, int n_blks, int rotate,
-                   int* __restrict__ err) {
+                   int kk, int tpb, int nstage, int fp16, int m_tiles, int n_blks, int* __restrict__ err) {
     pdl_wait();                 // nothing of global memory is touched before the predecessor has finished
     pdl_launch_dependents();    // the next kernel in the stream may begin its own launch now
     if (DGRAD && status != nullptr && (__ldg(status) & SVTAD_TABLE_ASYMMETRIC)) return;
@@ -616,7 +615,7 @@ static int launch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaStre
     int grid = (int)(tiles < tc_num_sms() ? tiles : tc_num_sms());
     SV_CUDA(tc_launch(kern, dim3(grid), dim3(HY_THREADS), smem, s, map_w, (const uint16_t*)p.a, p.nbr,
                       (const uint16_t*)p.bias, (uint16_t*)p.out, status, (long)p.n, cred, cn, p.kk, p.tpb, nstage, fp16,
-                      m_tiles, n_blks, 0, tc_error_ptr()));
+                      m_tiles, n_blks, tc_error_ptr()));
     return SVTAD_OK;
 }
 
