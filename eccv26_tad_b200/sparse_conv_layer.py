@@ -11,6 +11,11 @@ Differences, all additive:
   temporaries (implicit_gemm_v2.cu:361-414); nothing is materialised here;
 * the "indices are local to each batch row" heuristic (reference :170-177, a host sync on every
   call) is evaluated once per table object and cached, or skipped with ``local_indices=...``;
+* parameters kept in another dtype than the activations (fp32 masters under bf16 autocast) are cast once per
+  parameter version, not once per call (the reference casts on every forward, :196-203), and the backward is one
+  library call with the weight gradient running next to the input gradient;
+* checkpoints that hold the weight as ``(C_in, 9, C_out)`` are permuted on load (the reference does this in
+  ``opentad/utils/checkpoint.py:44-57``; ``remap_legacy_sparse_conv_weights`` is provided too);
 * the input gradient uses a gather form that needs a symmetric table (every table built by the
   backbone's code is).  Arbitrary tables are detected on the device by ``svtad_table_check`` and
   take the reference's scatter formulation, so results are defined for any table.
@@ -109,6 +114,45 @@ class SparseConv2dFunction(Function):
         return grad_input, None, grad_weight, grad_bias, None, None
 
 
+class _SparseConv2dCastFunction(Function):
+    """``SparseConv2dFunction`` for parameters kept in another dtype than the activations (autocast, or a bf16
+    input to an fp32 layer): the low-precision copies are made by the module (and cached there), the gradients
+    are handed back in the parameters' own dtype.  Same kernels, two autograd nodes fewer per call."""
+
+    @staticmethod
+    def forward(ctx, x, neighbor_indices, weight, bias, weight_c, bias_c, tokens_per_batch):
+        kk, C_in, C_out = weight_c.shape
+        if C_in % 4 != 0:
+            raise ValueError(f"C_in ({C_in}) must be divisible by 4 for optimized kernel.")
+        ctx.save_for_backward(x, neighbor_indices, weight_c)
+        ctx.C_in = C_in
+        ctx.tokens_per_batch = tokens_per_batch
+        ctx.param_dtype = weight.dtype
+        ctx.bias_dtype = bias.dtype if bias is not None else None
+        ctx.table_status = _status_for(neighbor_indices, tokens_per_batch) if ctx.needs_input_grad[0] else None
+        return ops.conv_fwd(x.reshape(-1, C_in), neighbor_indices.reshape(-1, kk), weight_c, bias_c, tokens_per_batch)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, neighbor_indices, weight_c = ctx.saved_tensors
+        kk = weight_c.shape[0]
+        tpb = ctx.tokens_per_batch
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[2]
+        need_b = ctx.bias_dtype is not None and ctx.needs_input_grad[3]
+        if not (need_x or need_w or need_b):
+            return None, None, None, None, None, None, None
+        status = None
+        if need_x:
+            status = ctx.table_status if ctx.table_status is not None else _status_for(neighbor_indices, tpb)
+        gx, gw, gb = ops.conv_bwd(grad_output, x.reshape(-1, ctx.C_in), neighbor_indices.reshape(-1, kk), weight_c, tpb,
+                                  table_status=status, need_x=need_x, need_w=need_w, need_b=need_b)
+        if gx is not None and x.dim() == 3:
+            gx = gx.view(x.shape)
+        gw = gw.to(ctx.param_dtype) if (need_w and gw is not None) else None
+        gb = gb.to(ctx.bias_dtype) if (need_b and gb is not None) else None
+        return gx, None, gw, gb, None, None, None
+
+
 class SparseConv2d(nn.Module):
     """Drop-in for the reference module (sparse_conv_layer.py:126-211)."""
 
@@ -166,24 +210,54 @@ class SparseConv2d(nn.Module):
 
         weight = self.weight
         bias = self.bias
+        target_dtype = x.dtype
         if torch.is_autocast_enabled():
             target_dtype = torch.get_autocast_dtype("cuda")
             if x.dtype != target_dtype:
                 x = x.to(target_dtype)
-            if weight.dtype != target_dtype:
-                weight = weight.to(target_dtype)
-            if bias is not None and bias.dtype != target_dtype:
-                bias = bias.to(target_dtype)
-        elif x.dtype != weight.dtype:
-            weight = weight.to(x.dtype)
-            if bias is not None:
-                bias = bias.to(x.dtype)
-
-        output = SparseConv2dFunction.apply(x, table, weight, bias, tokens_per_batch, self.chunk_size)
+        if weight.dtype == target_dtype and (bias is None or bias.dtype == target_dtype):
+            output = SparseConv2dFunction.apply(x, table, weight, bias, tokens_per_batch, self.chunk_size)
+        else:
+            # parameters live in another dtype (the usual case under autocast): their low-precision copies are
+            # kept until the parameters change, e.g. across the two forward passes of activation checkpointing
+            weight_c, bias_c = self._cast_params(target_dtype)
+            output = _SparseConv2dCastFunction.apply(x, table, weight, bias, weight_c, bias_c, tokens_per_batch)
         if is_batched:
             output = output.view(B, N, -1)
         return output
 
+    def _cast_params(self, dtype):
+        w, b = self.weight, self.bias
+        key = (dtype, w.data_ptr(), w._version, None if b is None else (b.data_ptr(), b._version))
+        cached = getattr(self, "_cast_cache", None)
+        if cached is None or cached[0] != key:
+            with torch.no_grad():
+                cached = (key, w.detach().to(dtype), None if b is None else b.detach().to(dtype))
+            self._cast_cache = cached
+        return cached[1], cached[2]
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        # older checkpoints hold the weight as (C_in, K*K, C_out); same rule as the reference's
+        # remap_legacy_sparse_conv_weights (opentad/utils/checkpoint.py:44-57)
+        key = prefix + "weight"
+        w = state_dict.get(key)
+        if w is not None and w.dim() == 3 and w.shape != self.weight.shape and \
+                w.permute(1, 0, 2).shape == self.weight.shape:
+            state_dict[key] = w.permute(1, 0, 2).contiguous()
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+
     def extra_repr(self):
         return (f"{self.in_channels}, {self.out_channels}, kernel_size={self.kernel_size}, "
                 f"bias={self.bias is not None}")
+
+
+def remap_legacy_sparse_conv_weights(state_dict, model_state_dict):
+    """Same contract as the reference helper (opentad/utils/checkpoint.py:44-57): every ``*sparse_conv.weight`` of
+    ``state_dict`` whose shape differs from the model's but matches after swapping the first two axes
+    (``(C_in, 9, C_out)`` -> ``(9, C_in, C_out)``) is permuted in place; the dict is returned."""
+    for key, param in state_dict.items():
+        if key.endswith("sparse_conv.weight") and key in model_state_dict:
+            target = model_state_dict[key].shape
+            if param.shape != target and param.dim() == 3 and param.permute(1, 0, 2).shape == target:
+                state_dict[key] = param.permute(1, 0, 2).contiguous()
+    return state_dict

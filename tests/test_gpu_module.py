@@ -66,6 +66,40 @@ def test_module_autocast_bf16_batched_local_and_global_indices():
         assert oconv.rel_err(f32np(m.bias.grad), egb) < 2e-2
 
 
+def test_autocast_parameter_copies_are_cached_until_the_parameters_change():
+    """The bf16 copies of fp32 parameters are made once per parameter version (two forwards of activation
+    checkpointing share them) and refreshed after an in-place update; gradients come back in fp32."""
+    from eccv26_tad_b200 import SparseConv2d, SparseConv2dFunction
+    _, _, table = make_table(1, 4, 14, 14, 0.3, 3, 41)
+    n = table.shape[0]
+    x, w, b, gy = make_conv_inputs(n, 64, 64, 3, torch.float32, 41, bias="random")
+    m = SparseConv2d(64, 64).cuda()
+    with torch.no_grad():
+        m.weight.copy_(w); m.bias.copy_(b)
+    tc, xc, gc = table.cuda(), x.cuda(), gy.cuda().bfloat16()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y1 = m(xc, tc)
+        w1 = m._cast_cache[1]
+        y2 = m(xc, tc)
+        assert m._cast_cache[1] is w1 and w1.dtype == torch.bfloat16
+        assert torch.equal(y1, y2)
+        # gradients equal those of the explicit-cast route through the reference-shaped Function
+        xa = xc.clone().requires_grad_(True)
+        m.zero_grad()
+        m(xa, tc).backward(gc)
+        xb = xc.clone().requires_grad_(True)
+        wr = m.weight.detach().clone().requires_grad_(True)
+        br = m.bias.detach().clone().requires_grad_(True)
+        SparseConv2dFunction.apply(xb.bfloat16(), tc, wr.bfloat16(), br.bfloat16(), 0, 0).backward(gc)
+        assert m.weight.grad.dtype == torch.float32 and torch.equal(m.weight.grad, wr.grad)
+        assert torch.equal(m.bias.grad, br.grad) and torch.equal(xa.grad, xb.grad)
+        with torch.no_grad():
+            m.weight.mul_(0.5)
+        y3 = m(xc, tc)
+        assert m._cast_cache[1] is not w1
+        assert not torch.equal(y3, y1)
+
+
 def test_function_apply_signature_and_partial_grads():
     from eccv26_tad_b200 import SparseConv2dFunction
     _, _, table = make_table(1, 2, 14, 14, 0.5, 3, 33)

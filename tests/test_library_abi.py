@@ -98,3 +98,29 @@ def test_shape_mismatches_raise_before_any_launch():
     with pytest.raises(ValueError):
         ops._check_shapes("conv_wgrad", 5, 9, nbr, grad_output=(torch.zeros(4, 8), 8))
     ops._check_shapes("conv_wgrad", 5, 9, nbr, grad_output=(torch.zeros(5, 8), 8))
+
+
+def test_legacy_checkpoint_layout_is_remapped_on_load():
+    """Weights stored as (C_in, 9, C_out) load into the (9, C_in, C_out) parameter, as with the reference's
+    remap_legacy_sparse_conv_weights (opentad/utils/checkpoint.py:44-57)."""
+    import torch
+    from eccv26_tad_b200 import SparseConv2d, remap_legacy_sparse_conv_weights
+
+    class Adapter(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.sparse_conv = SparseConv2d(8, 12)
+
+    src = Adapter()
+    legacy = {k: v.clone() for k, v in src.state_dict().items()}
+    legacy["sparse_conv.weight"] = legacy["sparse_conv.weight"].permute(1, 0, 2).contiguous()   # (C_in, 9, C_out)
+    assert legacy["sparse_conv.weight"].shape == (8, 9, 12)
+    dst = Adapter()
+    dst.load_state_dict({k: v.clone() for k, v in legacy.items()})
+    assert torch.equal(dst.sparse_conv.weight, src.sparse_conv.weight)
+    out = remap_legacy_sparse_conv_weights({k: v.clone() for k, v in legacy.items()}, Adapter().state_dict())
+    assert torch.equal(out["sparse_conv.weight"], src.sparse_conv.weight)
+    # current-layout checkpoints are left alone
+    dst2 = Adapter()
+    dst2.load_state_dict(src.state_dict())
+    assert torch.equal(dst2.sparse_conv.weight, src.sparse_conv.weight)
