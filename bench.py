@@ -20,7 +20,8 @@ Numbers on the JSON line
                forward / backward under autograd) with HOST buffers: every step copies scores,
                features and upstream gradients from pinned host memory and copies the outputs and
                all gradients back; the three keep rates run as three layers on three streams, so
-               copies in, kernels and copies out of different layers overlap
+               copies in, kernels and copies out of different layers overlap; the calls of a step are
+               captured into a CUDA graph per input set and replayed (eager if capture fails)
   roofline     the dominant kernel (largest share of device time among forward / dgrad / wgrad),
                dense-equivalent FLOPs 2*N*KK*Cin*Cout per launch over its CUDA-event duration,
                against the measured bf16 peak in MEASURED_PEAKS.json (fallback 1590 TFLOP/s)
@@ -437,7 +438,7 @@ def main():
     # One SparseConv2d per keep rate (three adapter layers with the same initial weights), each on its own
     # stream: copy in -> table -> forward -> backward -> copy out are ordered inside a layer's stream, and the
     # three layers' streams overlap one another, so the two copy engines and the SMs work at the same time.
-    # Host result buffers are double-buffered; a step waits for the copies of the step two before it.
+    # Every input set has its own pinned result buffers.
     modules = [SparseConv2d(C, C).to(dev) for _ in KEEPS]
     with torch.no_grad():
         for m in modules:
@@ -452,17 +453,15 @@ def main():
     out_h = [[{"y": torch.empty(it["n"], C, dtype=torch.bfloat16).pin_memory(),
                "gx": torch.empty(it["n"], C, dtype=torch.bfloat16).pin_memory(),
                "gw": torch.empty(KK, C, C, dtype=torch.float32).pin_memory(),
-               "gb": torch.empty(C, dtype=torch.float32).pin_memory()} for it in host_sets[0]] for _ in range(2)]
+               "gb": torch.empty(C, dtype=torch.float32).pin_memory()} for it in host_sets[0]] for _ in range(N_SETS)]
     h2d = sum(it["scores"].numel() * 4 + it["x"].numel() * 2 + it["gy"].numel() * 2 for it in host_sets[0])
     d2h = sum(2 * it["n"] * C * 2 for it in host_sets[0]) + 3 * (KK * C * C * 4 + C * 4)
     layer_streams = [torch.cuda.Stream(device=dev) for _ in KEEPS]
-    landed = [[None] * len(KEEPS) for _ in range(2)]
 
-    def e2e_step(si):
-        slot = si & 1
-        for ki, it in enumerate(pin[si % N_SETS]):
-            if landed[slot][ki] is not None:
-                landed[slot][ki].synchronize()
+    def e2e_body(si):
+        """One step's public-API calls, layer ki on layer_streams[ki]; results land in out_h[si % N_SETS]."""
+        slot = si % N_SETS
+        for ki, it in enumerate(pin[slot]):
             module = modules[ki]
             with torch.cuda.stream(layer_streams[ki]):
                 scores = it["scores"].to(dev, non_blocking=True)
@@ -481,13 +480,50 @@ def main():
                 o["gx"].copy_(x.grad, non_blocking=True)
                 o["gw"].copy_(module.weight.grad, non_blocking=True)
                 o["gb"].copy_(module.bias.grad, non_blocking=True)
-                ev = torch.cuda.Event()
-                ev.record()
-                landed[slot][ki] = ev
+
+    def fork_join(si):
+        """e2e_body between a fork from and a join back to the current stream."""
+        cur = torch.cuda.current_stream()
+        for st in layer_streams:
+            st.wait_stream(cur)
+        e2e_body(si)
+        for st in layer_streams:
+            cur.wait_stream(st)
+
+    # Steps alternate between two streams, so the copies in of one step overlap the copies out of the one before
+    # (with N > 1 a single stream keeps the ranks' collectives in one order).
+    step_streams = [torch.cuda.Stream(device=dev) for _ in range(2 if world == 1 else 1)]
+    for i in range(3):          # eager warm-up: allocator pools, cached parameter copies, the library's side stream
+        with torch.cuda.stream(step_streams[0]):
+            fork_join(i)
+    torch.cuda.synchronize()
+    # The step's calls are then captured once per input set (copies in, table, forward, backward, copies out) and
+    # replayed: a user with fixed shapes does the same, and the host's share of a step drops from ~1.2 ms of
+    # Python to one graph launch.  If capture is not possible the same calls are issued eagerly.
+    e2e_graphs = None
+    if not args.no_graph and os.environ.get("SVTAD_BENCH_E2E", "graph") != "eager":
+        try:
+            e2e_graphs = []
+            for si in range(N_SETS):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=step_streams[0]):
+                    fork_join(si)
+                e2e_graphs.append(g)
+        except Exception as e:
+            sys.stderr.write(f"[bench] e2e: CUDA graph capture failed ({str(e)[:200]}); issuing the calls eagerly\n")
+            e2e_graphs = None
+            torch.cuda.synchronize()
+
+    def e2e_step(si):
+        with torch.cuda.stream(step_streams[si % len(step_streams)]):
+            if e2e_graphs is not None:
+                e2e_graphs[si % N_SETS].replay()
+            else:
+                fork_join(si)
 
     def e2e_drain():
         cur = torch.cuda.current_stream()
-        for st in layer_streams:
+        for st in step_streams:
             cur.wait_stream(st)
 
     # Host-side copies on a shared machine are noisy (other tenants' PCIe and memory traffic): the timed steps
@@ -505,7 +541,7 @@ def main():
     for _ in range(E2E_BLOCKS):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for st in layer_streams:
+        for st in step_streams:
             st.wait_stream(torch.cuda.current_stream())
         for i in range(e2e_steps):
             e2e_step(step_no)
@@ -520,6 +556,14 @@ def main():
             ms = float(t.item())
         block_ms.append(ms)
     sampler.active = False
+    # what landed in host memory is what the resident path computes from the same inputs (same kernels: bitwise)
+    torch.cuda.synchronize()
+    chk = (step_no - 1) % N_SETS
+    for ki, it in enumerate(dsets[chk]):
+        y_ref = ops.conv_fwd(it["x"], it["table"], weight, bias)
+        gx_ref = ops.conv_dgrad(it["gy"], it["table"], weight, assume_symmetric=True)
+        assert torch.equal(out_h[chk][ki]["y"].to(dev), y_ref), "e2e forward output differs from the resident path"
+        assert torch.equal(out_h[chk][ki]["gx"].to(dev), gx_ref), "e2e input gradient differs from the resident path"
     e2e_ms = sorted(block_ms)[len(block_ms) // 2]
     e2e_value = world * tokens_step * e2e_steps / (e2e_ms * 1e-3)
     sampler.stop_flag = True
@@ -550,6 +594,7 @@ def main():
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
                     "stat": f"median of {E2E_BLOCKS} blocks of {e2e_steps} steps",
+                    "launch": "cuda_graph of the public-API calls" if e2e_graphs is not None else "eager",
                     "block_ms_per_step": [round(m / e2e_steps, 4) for m in block_ms]},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": roofline, "cpu_baseline": cpu, "reference_cuda": ref_cuda,
