@@ -28,6 +28,13 @@ namespace svtad {
 constexpr int HY_THREADS = 288;    // warps 0-3 producers, warp 4 MMA + TMEM owner, warps 5-8 epilogue
 constexpr int A_WARPS = 4;
 constexpr int A_THREADS = A_WARPS * 32;
+// forward / dgrad: producer warps, then the MMA warp, then four epilogue warps
+#ifndef SV_FW_A_WARPS
+#define SV_FW_A_WARPS 4
+#endif
+constexpr int FW_A_WARPS = SV_FW_A_WARPS;
+constexpr int FW_A_THREADS = FW_A_WARPS * 32;
+constexpr int FW_THREADS = (FW_A_WARPS + 5) * 32;
 
 // lane 0 waits (bounded), the whole warp learns the outcome
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* s_abort, int* err, int code,
@@ -44,7 +51,7 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 // ---------------------------------------------------------------------------------------------
 // RB = 64-deep buffers per barrier round (1 or 2).
 template <int BN, bool DGRAD, int RB>
-__global__ void __launch_bounds__(HY_THREADS, 1)
+__global__ void __launch_bounds__(FW_THREADS, 1)
 conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __restrict__ a,
                    const int32_t* __restrict__ nbr, const uint16_t* __restrict__ bias,
                    uint16_t* __restrict__ out, const int32_t* __restrict__ status, long n, int cred, int cn,
@@ -77,9 +84,13 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
     const int sp_pad = RB == 2 ? ((stages_per_tile + 1) & ~1) : stages_per_tile;
     const int nbig = nstage / RB;             // nstage (number of 64-deep buffers) is a multiple of RB
     constexpr int RSH = RB == 2 ? 1 : 0;      // buffer -> barrier round
+    // Producer warps that take turns on the buffers.  Never more than there are buffers: a warp only waits for
+    // the consumer on its own steps, so with more warps than buffers one of them could run two rounds ahead of
+    // the consumer, where the parity of the empty barrier looks the same as "free", and refill a buffer in use.
+    const int n_prod = nstage < FW_A_WARPS ? nstage : FW_A_WARPS;
     const int tab_ints = TILE_M * kk;
 
-    if (warp == 4) {
+    if (warp == FW_A_WARPS) {
         tmem_alloc(smem_u32(&tail->tmem_slot), TM_COLS);
         tmem_relinquish();
     }
@@ -103,7 +114,7 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
         const int valid_bytes = (int)rows * kk * 4;
         const char* src = reinterpret_cast<const char*>(nbr + row0 * kk);
         const uint32_t dst = smem_u32(s_tab);
-        for (int c = tid; c * 16 < tab_ints * 4; c += A_THREADS) {
+        for (int c = tid; c * 16 < tab_ints * 4; c += FW_A_THREADS) {
             int left = valid_bytes - c * 16;
             uint32_t nb = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
             cp_async16(dst + c * 16, nb ? src + c * 16 : src, nb);
@@ -111,13 +122,13 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
         cp_async_commit();
     };
     // the first tile's rows start their trip while the barriers and the tensor memory are set up
-    if (warp < A_WARPS && (int)blockIdx.x < tiles_total) load_table(blockIdx.x);
+    if (warp < FW_A_WARPS && (int)blockIdx.x < tiles_total) load_table(blockIdx.x);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tail->tmem_slot;
 
-    if (warp < A_WARPS) {
+    if (warp < FW_A_WARPS) {
         // ------------------------------------------------------------------ producers
         const int sub = lane & 7, rg = lane >> 3;
         bool alive = true;
@@ -129,27 +140,27 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
             // this tile's table rows have landed (only table copies are ever committed to a group); the first
             // barrier also says that every producer warp is done reading the previous tile's row numbers
             cp_async_wait<0>();
-            named_bar_sync(1, A_THREADS);
+            named_bar_sync(1, FW_A_THREADS);
             // entries become final row numbers: batch offset folded in, -1 for anything that reads as zero;
             // stored as [tap][row & 3][row >> 2], the order in which a lane group walks a stage's rows
-            for (int d = tid; d < tab_ints; d += A_THREADS) {
+            for (int d = tid; d < tab_ints; d += FW_A_THREADS) {
                 const int k = d >> 7, r = ((d & 31) << 2) | ((d >> 5) & 3);
                 long i = row0 + r;
                 int raw = s_tab[r * kk + k];
                 long jj = (long)raw + (tpb > 0 ? (i / tpb) * (long)tpb : 0);
                 xf[d] = (i < n && raw >= 0 && jj < n) ? (int)jj : -1;
             }
-            named_bar_sync(1, A_THREADS);
+            named_bar_sync(1, FW_A_THREADS);
             if (tile + (int)gridDim.x < tiles_total) load_table(tile + gridDim.x);
-            if (!alive) continue;   // keep taking part in the barriers above
+            if (!alive || warp >= n_prod) continue;   // keep taking part in the barriers above
             const int it0 = local * sp_pad;
-            // first step of this tile that this warp owns; then every A_WARPS-th one.  Buffer, phase and
+            // first step of this tile that this warp owns; then every n_prod-th one.  Buffer, phase and
             // (tap, chunk) advance incrementally: no division in the loop.
-            int st = (warp - it0) & (A_WARPS - 1);
+            int st = ((warp - it0) % n_prod + n_prod) % n_prod;
             int s = (it0 + st) % nstage;                         // 64-deep buffer; its barrier round is s >> 1
             uint32_t ph = (((it0 + st) / nstage) & 1) ^ 1;
             int k = st / kchunks, kc = st - k * kchunks;
-            for (; st < sp_pad; st += A_WARPS) {
+            for (; st < sp_pad; st += n_prod) {
                 if (!warp_wait(smem_u32(&tail->empty[s >> RSH]), ph, s_abort, err, 41, lane)) { alive = false; break; }
                 const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
                 const uint32_t bar = smem_u32(&tail->full[s >> RSH]);
@@ -191,14 +202,14 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                     }
                     cp_async_arrive_noinc(bar);
                 }
-                s += A_WARPS;
+                s += n_prod;
                 while (s >= nstage) { s -= nstage; ph ^= 1u; }
-                kc += A_WARPS;
+                kc += n_prod;
                 while (kc >= kchunks) { kc -= kchunks; if (++k == kk) k = 0; }
             }
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
-    } else if (warp == 4) {
+    } else if (warp == FW_A_WARPS) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = make_idesc(fp16 ? 0 : 1, 0, DGRAD ? 0 : 1, TILE_M, BN);
@@ -243,7 +254,7 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
         // ------------------------------------------------------------------ epilogue (warps 5..8)
         constexpr int NC = BN / 32;
         const int q = warp & 3;
-        const int et = tid - (A_WARPS + 1) * 32;          // 0..127 among the epilogue threads
+        const int et = tid - (FW_A_WARPS + 1) * 32;          // 0..127 among the epilogue threads
         float* s_bias = reinterpret_cast<float*>(s_tab + 2 * tab_ints);   // [2][256]
         int local = 0;
         for (int tile = blockIdx.x; tile < tiles_total; tile += gridDim.x, ++local) {
@@ -288,7 +299,7 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) {
+    if (warp == FW_A_WARPS) {
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, TM_COLS);
@@ -396,16 +407,18 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
             }
             cp_async_commit();
         };
-        if (warp < total_stages) load_rows(src_stage(warp), 0);
+        // never more producer warps than buffers (see the forward kernel)
+        const int n_prod = nstage < A_WARPS ? nstage : A_WARPS;
+        if (warp < total_stages && warp < n_prod) load_rows(src_stage(warp), 0);
         int local = 0;
         int s = warp % nstage;
         uint32_t ph = ((warp / nstage) & 1) ^ 1;
         const int rows = second_real ? 32 : 16;            // slots 64..127 belong to the second block
-        for (int it = warp; it < total_stages; it += A_WARPS, ++local) {
+        for (int it = warp; it < total_stages && warp < n_prod; it += n_prod, ++local) {
             const int* tab = my_tab + (local & 1) * tab_ints;
             cp_async_wait<0>();
             __syncwarp();
-            if (it + A_WARPS < total_stages) load_rows(src_stage(it + A_WARPS), (local & 1) ^ 1);
+            if (it + n_prod < total_stages) load_rows(src_stage(it + n_prod), (local & 1) ^ 1);
             // each lane turns four slots (slot = block * 64 + token) into final gather rows, the warp shares them
             // through shared memory, and every lane then holds the rows of the 32 slots it copies
             const long i0 = i_begin + (long)src_stage(it) * STAGE_K;
@@ -453,7 +466,7 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
                 }
             }
             cp_async_arrive_noinc(bar);
-            s += A_WARPS;
+            s += n_prod;
             while (s >= nstage) { s -= nstage; ph ^= 1u; }
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
@@ -613,7 +626,7 @@ static int launch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaStre
     const int n_blks = cn / BN;
     long tiles = (long)m_tiles * n_blks;
     int grid = (int)(tiles < tc_num_sms() ? tiles : tc_num_sms());
-    SV_CUDA(tc_launch(kern, dim3(grid), dim3(HY_THREADS), smem, s, map_w, (const uint16_t*)p.a, p.nbr,
+    SV_CUDA(tc_launch(kern, dim3(grid), dim3(FW_THREADS), smem, s, map_w, (const uint16_t*)p.a, p.nbr,
                       (const uint16_t*)p.bias, (uint16_t*)p.out, status, (long)p.n, cred, cn, p.kk, p.tpb, nstage, fp16,
                       m_tiles, n_blks, tc_error_ptr()));
     return SVTAD_OK;

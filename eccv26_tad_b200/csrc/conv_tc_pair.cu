@@ -153,6 +153,9 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
     // number of 64-deep steps gets an empty last half: its owner only arrives on the barrier.
     const int sp_pad = (stages_per_tile + 1) & ~1;
     const int nbig = nstage >> 1;             // nstage (number of 64-deep buffers) is even
+    // never more producer warps than buffers: a warp that is not held back by its own previous use of a buffer
+    // could run two rounds ahead of the consumer, where the empty barrier's parity reads as "free"
+    const int n_prod = nstage < PR_A_WARPS ? nstage : PR_A_WARPS;
     const int tab_ints = TILE_M * kk;
     float* s_bias = reinterpret_cast<float*>(s_tab + 2 * tab_ints);   // [2][256]
 
@@ -214,13 +217,13 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
             }
             named_bar_sync(1, PR_A_THREADS);
             if (item + n_clusters < items_total) load_table(item + n_clusters);
-            if (!alive) continue;
+            if (!alive || warp >= n_prod) continue;
             const int it0 = local * sp_pad;
-            int st = (warp - it0) & (PR_A_WARPS - 1);
+            int st = ((warp - it0) % n_prod + n_prod) % n_prod;
             int s = (it0 + st) % nstage;                         // 64-deep buffer; its barrier round is s >> 1
             uint32_t ph = (((it0 + st) / nstage) & 1) ^ 1;
             int k = st / kchunks, kc = st - k * kchunks;
-            for (; st < sp_pad; st += PR_A_WARPS) {
+            for (; st < sp_pad; st += n_prod) {
                 if (!warp_wait_pair(smem_u32(&tail->empty[s >> 1]), ph, s_abort, err, 51, lane)) { alive = false; break; }
                 const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
                 const uint32_t bar = smem_u32(&tail->full[s >> 1]);
@@ -259,9 +262,9 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
                     }
                     cp_async_arrive_noinc(bar);
                 }
-                s += PR_A_WARPS;
+                s += n_prod;
                 while (s >= nstage) { s -= nstage; ph ^= 1u; }
-                kc += PR_A_WARPS;
+                kc += n_prod;
                 while (kc >= kchunks) { kc -= kchunks; if (++k == kk) k = 0; }
             }
         }
