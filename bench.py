@@ -235,6 +235,8 @@ def main():
     ap.add_argument("--skip-ref-cuda", action="store_true")
     ap.add_argument("--workload", default="sparseconv", choices=["sparseconv", "backbone"],
                     help="backbone: forward of the ViT-B sparse-adapter backbone on 160-frame clips (secondary line)")
+    ap.add_argument("--backbone-train", action="store_true",
+                    help="with --workload backbone: one training step (forward, backward to the adapters, AdamW) per step")
     ap.add_argument("--kernel-case", default=None, choices=["fwd", "dgrad", "wgrad", "table"],
                     help="profiling aid: launch only this kernel a few times on --case-slices slices and exit")
     ap.add_argument("--case-slices", type=int, default=3840)
@@ -629,28 +631,57 @@ def backbone_case(args):
         torch.nn.init.normal_(blk.adapter.up_proj.weight, std=0.02)
     clips = [torch.randn(1, 3, 160, 224, 224, device=dev) for _ in range(2)]
     steps, warm = max(1, min(args.steps, 20)), max(3, min(args.warmup, 5))
-    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
-        for i in range(warm):
-            model(clips[i % 2])
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for i in range(steps):
-            out = model(clips[i % 2])
-        b.record()
-        torch.cuda.synchronize()
+    train = bool(args.backbone_train)
+    if train:
+        # SV-TAD's setting: frozen backbone, trainable adapters; gradients flow back through the frozen blocks
+        model.train()
+        for p in model.parameters():
+            p.requires_grad_(False)
+        params = [p for blk in model.blocks for p in blk.adapter.parameters()]
+        for p in params:
+            p.requires_grad_(True)
+        opt = torch.optim.AdamW(params, lr=1e-4)
+
+        def step(clip):
+            opt.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                out = model(clip)
+            out.float().square().mean().backward()
+            if world > 1:   # data parallel: one flat all-reduce of the adapters' gradients
+                flat = torch.cat([p.grad.reshape(-1) for p in params])
+                dist.all_reduce(flat)
+                off = 0
+                for p in params:
+                    p.grad.copy_(flat[off:off + p.numel()].view_as(p.grad) / world)
+                    off += p.numel()
+            opt.step()
+            return out
+    else:
+        def step(clip):
+            with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+                return model(clip)
+    for i in range(warm):
+        step(clips[i % 2])
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(steps):
+        out = step(clips[i % 2])
+    b.record()
+    torch.cuda.synchronize()
     ms = a.elapsed_time(b)
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     if rank == 0:
-        print(json.dumps({"metric": "sparse-adapter ViT-B backbone forward, clips/s", "value": world * steps / (ms * 1e-3),
+        what = "training step (forward, backward to the adapters, AdamW)" if train else "forward"
+        print(json.dumps({"metric": f"sparse-adapter ViT-B backbone {what}, clips/s", "value": world * steps / (ms * 1e-3),
                           "unit": "clips/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms / steps,
                           "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
-                          "config": {"workload": "ViT-B/16 sparse-adapter backbone forward, 3x160x224x224 clips, "
+                          "config": {"workload": f"ViT-B/16 sparse-adapter backbone {what}, 3x160x224x224 clips, "
                                                  "15680 tokens + CLS, adapters 768->192->768 with SparseConv2D 3x3, keep 30 % after block 3"},
                           "out_shape": list(out.shape)}))
     if world > 1:

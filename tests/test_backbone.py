@@ -59,3 +59,30 @@ def test_backbone_backward_reaches_adapter_parameters():
     for blk in sparse.blocks:
         g = blk.adapter.sparse_conv.weight.grad
         assert g is not None and torch.isfinite(g).all() and g.abs().sum() > 0
+
+
+@pytest.mark.gpu
+def test_adapter_gradients_match_dense_restatement_fp32():
+    """Training view: with the backbone frozen, the gradients that reach every adapter parameter through the
+    sparse path (SparseConv2d dgrad / wgrad + CUDA tables) equal those through scatter -> conv2d -> gather."""
+    dense, sparse = _models("cuda")
+    video = torch.randn(2, 3, 8, 64, 64, device="cuda")
+    grads = []
+    for model in (dense, sparse):
+        model.train()
+        for p in model.parameters():
+            p.requires_grad_(False)
+        names = []
+        for bi, blk in enumerate(model.blocks):
+            for n, p in blk.adapter.named_parameters():
+                p.requires_grad_(True)
+                names.append((f"blocks.{bi}.adapter.{n}", p))
+        out = model(video)
+        (out * torch.linspace(0.5, 1.5, out.numel(), device="cuda").view_as(out)).sum().backward()
+        grads.append({n: p.grad.clone() for n, p in names})
+    for n in grads[0]:
+        a, b = grads[0][n], grads[1][n]
+        assert a.shape == b.shape
+        scale = a.abs().max().item()
+        assert scale > 0, n
+        assert (a - b).abs().max().item() / scale < 2e-3, n
