@@ -1,6 +1,6 @@
 """Generates the golden fixtures in this directory.  Run only where the reference checkout exists:
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <checkout of pcr-upm/eccv26_tad>
 
 Table fixtures (``table_*.npz``) are outputs of the REFERENCE'S OWN SOURCE TEXT executed on
 CPU torch.  The backbone module cannot be imported (it imports mmcv / mmengine / mmaction at
