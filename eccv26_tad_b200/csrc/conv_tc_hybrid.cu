@@ -213,6 +213,7 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = make_idesc(fp16 ? 0 : 1, 0, DGRAD ? 0 : 1, TILE_M, BN);
+            constexpr uint32_t desc_hi = smem_desc_hi(1024);
             bool alive = true;
             int local = 0, s = 0;
             uint32_t ph = 0;
@@ -232,16 +233,16 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                     if (sn == nbig) { sn = 0; phn ^= 1u; }
                     ready = mbar_test_wait(smem_u32(&tail->full[sn]), phn);   // answer arrives while the MMAs issue
                     const int halves = (RB == 2 && st + 1 < stages_per_tile) ? 2 : 1;
+                    // descriptor low words: start address >> 4 (shared memory is below 256 KB, so adding a K step's
+                    // offset never carries into the LBO field above it)
+                    uint32_t a_lo = (a_tile & 0x3FFFFu) >> 4;
                     for (int h = 0; h < halves; ++h) {
-                        const uint32_t a_h = a_tile + (uint32_t)h * STAGE_BYTES;
-                        const uint32_t b_h = a_h + A_TILE_BYTES;
+                        const uint32_t b_lo = (a_lo + (A_TILE_BYTES >> 4)) | (DGRAD ? 0u : smem_desc_lbo_bits(8192));
 #pragma unroll
-                        for (int ks = 0; ks < STAGE_K / 16; ++ks) {
-                            uint64_t ad = make_smem_desc(a_h + ks * 32, 0, 1024);
-                            uint64_t bd = DGRAD ? make_smem_desc(b_h + ks * 32, 0, 1024)
-                                                : make_smem_desc(b_h + ks * 2048, 8192, 1024);
-                            umma_f16(d_tmem, ad, bd, idesc, (st | h | ks) != 0 ? 1u : 0u);
-                        }
+                        for (int ks = 0; ks < STAGE_K / 16; ++ks)
+                            umma_f16_lh(d_tmem, a_lo + ks * 2, desc_hi, b_lo + ks * (DGRAD ? 2 : 128), desc_hi, idesc,
+                                        (st | h | ks) != 0 ? 1u : 0u);
+                        a_lo += STAGE_BYTES >> 4;
                     }
                     umma_commit(smem_u32(&tail->empty[s]));
                     s = sn;
