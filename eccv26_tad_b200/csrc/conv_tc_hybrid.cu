@@ -483,17 +483,17 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
                 fence_proxy_async();
                 tc_fence_after();
                 const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
-                const uint32_t b_tile = a_tile + A_TILE_BYTES;
                 int sn = s + 1;
                 uint32_t phn = ph;
                 if (sn == nstage) { sn = 0; phn ^= 1u; }
                 ready = mbar_test_wait(smem_u32(&tail->full[sn]), phn);
+                // both operands MN-major: 16 K rows per step = 2048 B, 64-element blocks 8192 B apart
+                const uint32_t a_lo = ((a_tile & 0x3FFFFu) >> 4) | smem_desc_lbo_bits(8192);
+                const uint32_t b_lo = a_lo + (A_TILE_BYTES >> 4);
 #pragma unroll
-                for (int ks = 0; ks < STAGE_K / 16; ++ks) {
-                    uint64_t ad = make_smem_desc(a_tile + ks * 2048, 8192, 1024);
-                    uint64_t bd = make_smem_desc(b_tile + ks * 2048, 8192, 1024);
-                    umma_f16(tmem_base, ad, bd, idesc, (it | ks) != 0 ? 1u : 0u);
-                }
+                for (int ks = 0; ks < STAGE_K / 16; ++ks)
+                    umma_f16_lh(tmem_base, a_lo + ks * 128, smem_desc_hi(1024), b_lo + ks * 128, smem_desc_hi(1024), idesc,
+                                (it | ks) != 0 ? 1u : 0u);
                 umma_commit(smem_u32(&tail->empty[s]));
                 s = sn;
                 ph = phn;

@@ -79,28 +79,21 @@ __device__ __forceinline__ void tmem_relinquish_pair() {
 __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
     asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
-__device__ __forceinline__ void umma_pair_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+// tcgen05.mma over the CTA pair; descriptors as (low word, high word)
+__device__ __forceinline__ void umma_pair_f16_lh(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                                 uint32_t idesc, uint32_t accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 // arrival on a barrier of either CTA (cluster address) once every MMA issued so far by this thread has finished
 __device__ __forceinline__ void umma_pair_commit(uint32_t cluster_addr) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
 }
-// shared-memory matrix descriptor with an explicit layout code (2 = 128-byte swizzle, 4 = 64-byte swizzle)
-__device__ __forceinline__ uint64_t make_smem_desc_layout(uint32_t saddr, uint32_t lbo, uint32_t sbo, uint32_t layout) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
-    d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16;
-    d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32;
-    d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(layout) << 61;
-    return d;
-}
-
 // lane 0 waits (bounded), the whole warp learns the outcome
 __device__ __forceinline__ bool warp_wait_pair(uint32_t bar, uint32_t parity, volatile int* s_abort, int* err, int code,
                                                int lane) {
@@ -294,17 +287,19 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
                     if (sn == nbig) { sn = 0; phn ^= 1u; }
                     ready = mbar_test_wait(smem_u32(&tail->full[sn]), phn);
                     const int halves = (st + 1 < stages_per_tile) ? 2 : 1;
+                    // descriptor low words (start address >> 4, LBO field); the high words are constants.
+                    // forward B: 16 K rows of 64 B per step (1024 B), 8-row groups 512 B apart, 32-column atoms
+                    // 4 KB apart, 64-byte swizzle (layout code 4)
+                    uint32_t a_lo = (a_tile & 0x3FFFFu) >> 4;
+                    constexpr uint32_t a_hi = smem_desc_hi(1024);
+                    constexpr uint32_t b_hi = DGRAD ? smem_desc_hi(1024) : (((512u >> 4) & 0x3FFFu) | (1u << 14) | (4u << 29));
                     for (int h = 0; h < halves; ++h) {
-                        const uint32_t a_h = a_tile + (uint32_t)h * STAGE_BYTES;
-                        const uint32_t b_h = a_h + A_TILE_BYTES;
+                        const uint32_t b_lo = (a_lo + (A_TILE_BYTES >> 4)) | (DGRAD ? 0u : smem_desc_lbo_bits(4096));
 #pragma unroll
-                        for (int ks = 0; ks < STAGE_K / 16; ++ks) {
-                            uint64_t ad = make_smem_desc(a_h + ks * 32, 0, 1024);
-                            // forward: 16 K rows of 64 B per step, 8-row groups 512 B apart, 32-column atoms 4 KB apart
-                            uint64_t bd = DGRAD ? make_smem_desc(b_h + ks * 32, 0, 1024)
-                                                : make_smem_desc_layout(b_h + ks * 1024, 4096, 512, 4);
-                            umma_pair_f16(d_tmem, ad, bd, idesc, (st | h | ks) != 0 ? 1u : 0u);
-                        }
+                        for (int ks = 0; ks < STAGE_K / 16; ++ks)
+                            umma_pair_f16_lh(d_tmem, a_lo + ks * 2, a_hi, b_lo + ks * (DGRAD ? 2 : 64), b_hi, idesc,
+                                             (st | h | ks) != 0 ? 1u : 0u);
+                        a_lo += STAGE_BYTES >> 4;
                     }
                     const uint32_t e_local = smem_u32(&tail->empty[s]);
                     umma_pair_commit(e_local);
