@@ -226,7 +226,6 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                 for (int st = 0; st < sp_pad; st += RB) {
                     if (!ready && !mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 43)) { alive = false; break; }
                     fence_proxy_async();   // cp.async (generic proxy) writes -> tcgen05.mma (async proxy) reads
-                    tc_fence_after();
                     const uint32_t a_tile = stage_base + (uint32_t)(RB * s) * STAGE_BYTES;
                     int sn = s + 1;
                     uint32_t phn = ph;
@@ -238,10 +237,10 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                     uint32_t a_lo = (a_tile & 0x3FFFFu) >> 4;
                     for (int h = 0; h < halves; ++h) {
                         const uint32_t b_lo = (a_lo + (A_TILE_BYTES >> 4)) | (DGRAD ? 0u : smem_desc_lbo_bits(8192));
+                        umma_f16_lh(d_tmem, a_lo, desc_hi, b_lo, desc_hi, idesc, (st | h) != 0 ? 1u : 0u);
 #pragma unroll
-                        for (int ks = 0; ks < STAGE_K / 16; ++ks)
-                            umma_f16_lh(d_tmem, a_lo + ks * 2, desc_hi, b_lo + ks * (DGRAD ? 2 : 128), desc_hi, idesc,
-                                        (st | h | ks) != 0 ? 1u : 0u);
+                        for (int ks = 1; ks < STAGE_K / 16; ++ks)
+                            umma_f16_lh_acc(d_tmem, a_lo + ks * 2, desc_hi, b_lo + ks * (DGRAD ? 2 : 128), desc_hi, idesc);
                         a_lo += STAGE_BYTES >> 4;
                     }
                     umma_commit(smem_u32(&tail->empty[s]));
@@ -481,7 +480,6 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
             for (int it = 0; it < total_stages; ++it) {
                 if (!ready && !mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 52)) { alive = false; break; }
                 fence_proxy_async();
-                tc_fence_after();
                 const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
                 int sn = s + 1;
                 uint32_t phn = ph;
@@ -490,10 +488,10 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
                 // both operands MN-major: 16 K rows per step = 2048 B, 64-element blocks 8192 B apart
                 const uint32_t a_lo = ((a_tile & 0x3FFFFu) >> 4) | smem_desc_lbo_bits(8192);
                 const uint32_t b_lo = a_lo + (A_TILE_BYTES >> 4);
+                umma_f16_lh(tmem_base, a_lo, smem_desc_hi(1024), b_lo, smem_desc_hi(1024), idesc, it != 0 ? 1u : 0u);
 #pragma unroll
-                for (int ks = 0; ks < STAGE_K / 16; ++ks)
-                    umma_f16_lh(tmem_base, a_lo + ks * 128, smem_desc_hi(1024), b_lo + ks * 128, smem_desc_hi(1024), idesc,
-                                (it | ks) != 0 ? 1u : 0u);
+                for (int ks = 1; ks < STAGE_K / 16; ++ks)
+                    umma_f16_lh_acc(tmem_base, a_lo + ks * 128, smem_desc_hi(1024), b_lo + ks * 128, smem_desc_hi(1024), idesc);
                 umma_commit(smem_u32(&tail->empty[s]));
                 s = sn;
                 ph = phn;

@@ -280,7 +280,6 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
                 for (int st = 0; st < sp_pad; st += 2) {
                     if (!ready && !mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 53)) { alive = false; break; }
                     fence_proxy_async();
-                    tc_fence_after();
                     const uint32_t a_tile = stage_base + (uint32_t)(2 * s) * STAGE_BYTES;
                     int sn = s + 1;
                     uint32_t phn = ph;
@@ -298,7 +297,7 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
 #pragma unroll
                         for (int ks = 0; ks < STAGE_K / 16; ++ks)
                             umma_pair_f16_lh(d_tmem, a_lo + ks * 2, a_hi, b_lo + ks * (DGRAD ? 2 : 64), b_hi, idesc,
-                                             (st | h | ks) != 0 ? 1u : 0u);
+                                             ks != 0 ? 1u : ((st | h) != 0 ? 1u : 0u));
                         a_lo += STAGE_BYTES >> 4;
                     }
                     const uint32_t e_local = smem_u32(&tail->empty[s]);

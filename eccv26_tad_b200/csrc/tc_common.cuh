@@ -107,6 +107,17 @@ __device__ __forceinline__ void umma_f16_lh(uint32_t d_tmem, uint32_t a_lo, uint
         "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
         ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
+// accumulating form (D += A.B) with the predicate set once, for every K step but a tile's first
+__device__ __forceinline__ void umma_f16_lh_acc(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                                uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\t"
+        "mov.b64 db, {%3, %4};\n\t"
+        "setp.eq.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc) : "memory");
+}
 // high word of a 128-byte-swizzle descriptor (SBO, version 1, layout code 2) and the LBO bits of the low word
 __host__ __device__ constexpr uint32_t smem_desc_hi(uint32_t sbo) { return ((sbo >> 4) & 0x3FFFu) | (1u << 14) | (2u << 29); }
 __host__ __device__ constexpr uint32_t smem_desc_lbo_bits(uint32_t lbo) { return ((lbo >> 4) & 0x3FFFu) << 16; }
