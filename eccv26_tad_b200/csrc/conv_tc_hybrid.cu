@@ -90,6 +90,25 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
     const int n_prod = nstage < FW_A_WARPS ? nstage : FW_A_WARPS;
     const int tab_ints = TILE_M * kk;
 
+    // raw table rows of a tile -> s_tab, by the producer threads, one tile ahead.  Behind them goes an L2 prefetch
+    // of the rows the tile will gather: for tables built on a grid they lie within a few dozen rows of the tile's
+    // own, so the gathers that follow the table's trip to memory do not have to make a second one.
+    auto load_table = [&](int tile) {
+        const long row0 = (long)(tile / n_blks) * TILE_M;
+        const long rows = (n - row0) < TILE_M ? (n - row0) : TILE_M;
+        const int valid_bytes = (int)rows * kk * 4;
+        const char* src = reinterpret_cast<const char*>(nbr + row0 * kk);
+        const uint32_t dst = smem_u32(s_tab);
+        for (int c = tid; c * 16 < tab_ints * 4; c += FW_A_THREADS) {
+            int left = valid_bytes - c * 16;
+            uint32_t nb = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
+            cp_async16(dst + c * 16, nb ? src + c * 16 : src, nb);
+        }
+        cp_async_commit();
+        if (tid == FW_A_THREADS - 1) l2_prefetch_rows(a, row0 - 64, row0 + TILE_M + 64, n, cred);
+    };
+    // the first tile's rows start their trip before anything else is set up
+    if (warp < FW_A_WARPS && (int)blockIdx.x < tiles_total) load_table(blockIdx.x);
     if (warp == FW_A_WARPS) {
         tmem_alloc(smem_u32(&tail->tmem_slot), TM_COLS);
         tmem_relinquish();
@@ -107,22 +126,6 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
         fence_mbar_init();
         tma_prefetch_map(&map_w);
     }
-    // raw table rows of a tile -> s_tab, by the producer threads, one tile ahead
-    auto load_table = [&](int tile) {
-        const long row0 = (long)(tile / n_blks) * TILE_M;
-        const long rows = (n - row0) < TILE_M ? (n - row0) : TILE_M;
-        const int valid_bytes = (int)rows * kk * 4;
-        const char* src = reinterpret_cast<const char*>(nbr + row0 * kk);
-        const uint32_t dst = smem_u32(s_tab);
-        for (int c = tid; c * 16 < tab_ints * 4; c += FW_A_THREADS) {
-            int left = valid_bytes - c * 16;
-            uint32_t nb = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
-            cp_async16(dst + c * 16, nb ? src + c * 16 : src, nb);
-        }
-        cp_async_commit();
-    };
-    // the first tile's rows start their trip while the barriers and the tensor memory are set up
-    if (warp < FW_A_WARPS && (int)blockIdx.x < tiles_total) load_table(blockIdx.x);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();

@@ -205,6 +205,16 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar) : "memory");
 }
+// hint: bring `bytes` (multiple of 16) starting at the 16-byte aligned `p` into L2; no completion to wait for
+__device__ __forceinline__ void l2_prefetch_bulk(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+// rows [row_lo, row_hi) of a row-major 16-bit matrix with `cols` columns, clipped to [0, n)
+__device__ __forceinline__ void l2_prefetch_rows(const uint16_t* base, long row_lo, long row_hi, long n, int cols) {
+    if (row_lo < 0) row_lo = 0;
+    if (row_hi > n) row_hi = n;
+    if (row_hi > row_lo) l2_prefetch_bulk(base + row_lo * cols, (uint32_t)((row_hi - row_lo) * cols * 2));
+}
 __device__ __forceinline__ void tma_prefetch_map(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
