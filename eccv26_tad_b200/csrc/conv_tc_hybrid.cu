@@ -346,6 +346,38 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
     // second block of the last pair when the block count is odd: all ones, so its rows of D are sum_i gy[i,:]
     const bool ones_here = ones_block && !second_real;
 
+    // table rows of a warp's 64-token step, double buffered: [2][STAGE_K * kk] ints per warp
+    const int tab_ints = STAGE_K * kk;
+    int* my_tab = s_idx + warp * (2 * tab_ints + TILE_M);
+    int* my_rows = my_tab + 2 * tab_ints;              // [TILE_M] final gather rows of the current step
+    // CTAs of different block pairs walk the token range from different starting points (see the
+    // forward kernel); `src_stage` is the 64-token step that pipeline step `it` carries
+    const int rot = (rotate && total_stages > 0) ? (int)(((long)blockIdx.x * 5) % total_stages) : 0;
+    auto src_stage = [&](int it) { int v = it + rot; return v >= total_stages ? v - total_stages : v; };
+    // the step's table rows are contiguous in memory: copy them whole (16-byte cp.async, rows past the
+    // end of this split read as zero bytes) one warp-iteration ahead; only these copies are committed
+    auto load_rows = [&](int sit, int buf) {
+        const long i0 = i_begin + (long)sit * STAGE_K;
+        const long rows = (i_end - i0) < STAGE_K ? (i_end - i0) : STAGE_K;
+        const int valid_bytes = (int)rows * kk * 4;
+        const char* src = reinterpret_cast<const char*>(nbr + i0 * kk);
+        const uint32_t dst = smem_u32(my_tab + buf * tab_ints);
+        for (int c = lane; c * 16 < tab_ints * 4; c += 32) {
+            int left = valid_bytes - c * 16;
+            uint32_t nb = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
+            cp_async16(dst + c * 16, nb ? src + c * 16 : src, nb);
+        }
+        cp_async_commit();
+    };
+    // never more producer warps than buffers (see the forward kernel)
+    const int n_prod = nstage < A_WARPS ? nstage : A_WARPS;
+    // the first step's rows start their trip before anything else is set up
+    if (warp < A_WARPS && warp < total_stages && warp < n_prod) {
+        load_rows(src_stage(warp), 0);
+        // and an L2 prefetch of the rows that step will gather (within a few dozen rows of its own tokens)
+        const long i0 = i_begin + (long)src_stage(warp) * STAGE_K;
+        if (lane == 31) l2_prefetch_rows(x, i0 - 64, i0 + STAGE_K + 64, n, cin);
+    }
     if (warp == 4) {
         tmem_alloc(smem_u32(&tail->tmem_slot), TM_COLS);
         tmem_relinquish();
@@ -386,33 +418,7 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
             tap[h] = real ? blk / cblocks : 0;
             ch0[h] = real ? (blk % cblocks) * 64 : 0;
         }
-        // table rows of a warp's 64-token step, double buffered: [2][STAGE_K * kk] ints per warp
-        const int tab_ints = STAGE_K * kk;
-        int* my_tab = s_idx + warp * (2 * tab_ints + TILE_M);
-        int* my_rows = my_tab + 2 * tab_ints;              // [TILE_M] final gather rows of the current step
         const int sub = lane & 7, rg = lane >> 3;
-        // CTAs of different block pairs walk the token range from different starting points (see the
-        // forward kernel); `src_stage` is the 64-token step that pipeline step `it` carries
-        const int rot = (rotate && total_stages > 0) ? (int)(((long)blockIdx.x * 5) % total_stages) : 0;
-        auto src_stage = [&](int it) { int v = it + rot; return v >= total_stages ? v - total_stages : v; };
-        // the step's table rows are contiguous in memory: copy them whole (16-byte cp.async, rows past the
-        // end of this split read as zero bytes) one warp-iteration ahead; only these copies are committed
-        auto load_rows = [&](int sit, int buf) {
-            const long i0 = i_begin + (long)sit * STAGE_K;
-            const long rows = (i_end - i0) < STAGE_K ? (i_end - i0) : STAGE_K;
-            const int valid_bytes = (int)rows * kk * 4;
-            const char* src = reinterpret_cast<const char*>(nbr + i0 * kk);
-            const uint32_t dst = smem_u32(my_tab + buf * tab_ints);
-            for (int c = lane; c * 16 < tab_ints * 4; c += 32) {
-                int left = valid_bytes - c * 16;
-                uint32_t nb = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
-                cp_async16(dst + c * 16, nb ? src + c * 16 : src, nb);
-            }
-            cp_async_commit();
-        };
-        // never more producer warps than buffers (see the forward kernel)
-        const int n_prod = nstage < A_WARPS ? nstage : A_WARPS;
-        if (warp < total_stages && warp < n_prod) load_rows(src_stage(warp), 0);
         int local = 0;
         int s = warp % nstage;
         uint32_t ph = ((warp / nstage) & 1) ^ 1;

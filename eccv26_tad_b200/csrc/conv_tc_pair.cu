@@ -152,6 +152,24 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
     const int tab_ints = TILE_M * kk;
     float* s_bias = reinterpret_cast<float*>(s_tab + 2 * tab_ints);   // [2][256]
 
+    auto load_table = [&](int item) {
+        const long row0 = ((long)(item / n_blks) * 2 + rank) * TILE_M;
+        long rows = n - row0;
+        rows = rows < 0 ? 0 : (rows < TILE_M ? rows : TILE_M);
+        const int valid_bytes = (int)rows * kk * 4;
+        const char* src = reinterpret_cast<const char*>(nbr + (rows > 0 ? row0 : 0) * kk);
+        const uint32_t dst = smem_u32(s_tab);
+        for (int c = tid; c * 16 < tab_ints * 4; c += PR_A_THREADS) {
+            int left = valid_bytes - c * 16;
+            uint32_t nb = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
+            cp_async16(dst + c * 16, nb ? src + c * 16 : src, nb);
+        }
+        cp_async_commit();
+        // L2 prefetch of the rows this tile will gather (see the one-CTA kernel)
+        if (tid == PR_A_THREADS - 1) l2_prefetch_rows(a, row0 - 64, row0 + TILE_M + 64, n, cred);
+    };
+    // the first tile's rows start their trip before anything else is set up
+    if (warp < PR_A_WARPS && cid < items_total) load_table(cid);
     if (warp == 4) {
         tmem_alloc_pair(smem_u32(&tail->tmem_slot), TM_COLS);
         tmem_relinquish_pair();
@@ -169,21 +187,6 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
         fence_mbar_init();
         tma_prefetch_map(&map_w);
     }
-    auto load_table = [&](int item) {
-        const long row0 = ((long)(item / n_blks) * 2 + rank) * TILE_M;
-        long rows = n - row0;
-        rows = rows < 0 ? 0 : (rows < TILE_M ? rows : TILE_M);
-        const int valid_bytes = (int)rows * kk * 4;
-        const char* src = reinterpret_cast<const char*>(nbr + (rows > 0 ? row0 : 0) * kk);
-        const uint32_t dst = smem_u32(s_tab);
-        for (int c = tid; c * 16 < tab_ints * 4; c += PR_A_THREADS) {
-            int left = valid_bytes - c * 16;
-            uint32_t nb = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
-            cp_async16(dst + c * 16, nb ? src + c * 16 : src, nb);
-        }
-        cp_async_commit();
-    };
-    if (warp < PR_A_WARPS && cid < items_total) load_table(cid);
     tc_fence_before();
     __syncthreads();
     cluster_barrier();          // both CTAs' barriers exist before anyone arrives on the other's
