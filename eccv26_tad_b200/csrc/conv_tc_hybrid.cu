@@ -16,9 +16,15 @@
 //
 // Forward / dgrad CTAs are persistent over (row tile, column block) work items with two accumulators in
 // tensor memory, so a tile's epilogue overlaps the next tile's main loop; the tile's table rows are
-// prefetched into shared memory one tile ahead.  No TMA load uses cluster multicast.  Every mbarrier wait
-// is bounded: when it runs out the CTA records a code in the device error word, stops, frees its tensor
-// memory and returns.
+// prefetched into shared memory one tile ahead (with an L2 prefetch of the rows it will gather) and rewritten
+// there as final row numbers in the order the producer lanes read them.  Where at least three rounds fit in
+// shared memory, two 64-deep buffers share one full / empty barrier pair, so the issuing thread's per-round
+// work is spent once per eight MMAs.  At most min(producer warps, buffers) warps produce: a warp waits for the
+// consumer only on its own steps, and with more warps than buffers it could lap the consumer by two rounds,
+// which the barrier's phase parity cannot tell from "free".  No TMA load uses cluster multicast.  Every
+// mbarrier wait is bounded: when it runs out the CTA records a code in the device error word, stops, frees its
+// tensor memory and returns.  Inputs whose row tiles outnumber the SMs go to the CTA-pair kernels instead
+// (conv_tc_pair.cu).
 #include <cstdlib>
 
 #include "tc_common.cuh"
