@@ -20,7 +20,6 @@ activation checkpointing) are left out.
 ``table_impl`` selects who maintains the table: "svtad" (CUDA kernels) or "torch" (the reference's
 tensor ops restated, for checking).
 """
-import math
 
 import torch
 import torch.nn as nn

@@ -6,8 +6,6 @@ Counterparts in ``opentad/models/backbones/vit_sparse_adapter_poguise.py``:
 """
 import math
 
-import torch
-
 from . import ops
 
 
