@@ -54,6 +54,21 @@ def test_host_side_validation_returns_codes():
     assert rc == _lib.ERR_ARG and "odd" in _lib.last_error()
     with pytest.raises(ValueError):
         _lib.check(rc)
+    # the one-call backward: something must be asked for, a bias gradient needs the weight gradient
+    rc = lib.svtad_conv_bwd(None, None, None, None, None, None, None, 4, 8, 8, 9, 0, _lib.F32, None, None, 0, None)
+    assert rc == _lib.ERR_ARG and "neither" in _lib.last_error()
+    rc = lib.svtad_conv_bwd(None, None, None, None, 1, None, 1, 4, 8, 8, 9, 0, _lib.F32, None, None, 0, None)
+    assert rc == _lib.ERR_ARG and "gb needs gw" in _lib.last_error()
+    # fused selection + remap of a later round
+    rc = lib.svtad_table_select_remap(None, None, 2, 100, 101, 9, None, None, None, None)
+    assert rc == _lib.ERR_ARG and "k_keep" in _lib.last_error()
+    rc = lib.svtad_table_select_remap(None, None, 2, 100, 50, 9, None, None, None, None)
+    assert rc == _lib.ERR_ARG and "null" in _lib.last_error()
+    rc = lib.svtad_table_select_remap(1, 1, 2, 60000, 50, 9, 1, None, 1, None)
+    assert rc == _lib.ERR_UNSUPPORTED and "limit" in _lib.last_error()
+    assert lib.svtad_table_select_remap(None, None, 0, 100, 50, 9, None, None, None, None) == 0
+    assert lib.svtad_workspace_bytes(_lib.OP_BWD, 9440, 192, 192, 9, _lib.BF16) >= \
+        lib.svtad_workspace_bytes(_lib.OP_WGRAD, 9440, 192, 192, 9, _lib.BF16) + 9440 * 192 * 4
     # empty problems are fine and touch nothing
     assert lib.svtad_conv_fwd(None, None, None, None, None, 0, 8, 8, 9, 0, _lib.F32, None, 0, None) == 0
     assert lib.svtad_table_init(0, 8, 14, 14, 3, None, None) == 0
