@@ -53,7 +53,7 @@ FALLBACK_HBM = 6650.0
 METRIC = "SparseConv2D retained tokens/sec fwd+bwd at keep 10-55%"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised under profiles/
 # (226 560-row case, C=192), divided by the rows of that launch; traffic grows in proportion to the rows
-NCU_DRAM_BYTES_PER_ROW = {"fwd": 136.57e6 / 226560, "dgrad": 136.12e6 / 226560, "wgrad": 233.35e6 / 226560}
+NCU_DRAM_BYTES_PER_ROW = {"fwd": 136.85e6 / 226560, "dgrad": 137.57e6 / 226560, "wgrad": 241.24e6 / 226560}
 
 
 def flops_pass(n):
