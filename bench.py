@@ -290,7 +290,15 @@ def main():
     # one flat bucket for the gradients of the step's three layers (gw ++ gb each), all-reduced once per step
     # the way DDP buckets the adapters' gradients (reference: src/eccv26_tad.py:288-300, 25 MB buckets)
     per_layer = KK * C * C + C
-    grads = torch.empty(len(KEEPS) * per_layer, dtype=torch.bfloat16, device=dev)
+    n_grads = len(KEEPS) * per_layer
+    # N > 1: the bucket sits in symmetric memory and is summed by a two-shot all-reduce over NVLink peer loads
+    # (GradBucket falls back to NCCL where that cannot be set up; SVTAD_BENCH_ALLREDUCE=nccl forces NCCL)
+    from eccv26_tad_b200.distributed import GradBucket
+    bucket = GradBucket(n_grads, torch.bfloat16, dev,
+                        allow_symmetric=os.environ.get("SVTAD_BENCH_ALLREDUCE", "symm") != "nccl")
+    grads, allreduce_kind = bucket.buffer, bucket.kind
+    if world > 1 and bucket.kind == "nccl" and hasattr(bucket, "fallback_reason"):
+        sys.stderr.write(f"[bench] symmetric-memory all-reduce unavailable ({bucket.fallback_reason}); using NCCL\n")
     gw_bufs = [grads[i * per_layer:i * per_layer + KK * C * C] for i in range(len(KEEPS))]
     gb_bufs = [grads[i * per_layer + KK * C * C:(i + 1) * per_layer] for i in range(len(KEEPS))]
     gw_buf, gb_buf = gw_bufs[0], gb_bufs[0]
@@ -318,7 +326,7 @@ def main():
             cur.wait_stream(side)
             nl += 4   # fwd, dgrad, wgrad partials (bias row included), reduce
         if world > 1:
-            dist.all_reduce(grads)
+            bucket.all_reduce()
         return nl
 
     stream = torch.cuda.Stream(device=dev)
@@ -592,7 +600,8 @@ def main():
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": dict(workload_config(world), launch="cuda_graph" if graphs is not None else "eager"),
+            "config": dict(workload_config(world), launch="cuda_graph" if graphs is not None else "eager",
+                           **({"allreduce": allreduce_kind} if world > 1 else {})),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
                     "stat": f"median of {E2E_BLOCKS} blocks of {e2e_steps} steps",

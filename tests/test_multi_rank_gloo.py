@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from eccv26_tad_b200.distributed import allreduce_weight_grads, shard_clips
+from eccv26_tad_b200.distributed import GradBucket, allreduce_weight_grads, shard_clips
 from oracle import conv as oconv
 from oracle import table as otab
 
@@ -42,6 +42,13 @@ def _worker(rank, world, port, out):
         gx = oconv.dgrad(gy[lo:hi], tab, w)
         gw, gb = oconv.wgrad(gy[lo:hi], x[lo:hi], tab, 9)
         gw_t, gb_t = allreduce_weight_grads(torch.from_numpy(gw), torch.from_numpy(gb))
+        # the same sum through the bucket object (on CPU / gloo it is an ordinary tensor + dist.all_reduce)
+        bucket = GradBucket(gw.size + gb.size, torch.float64, "cpu")
+        bucket.view(0, gw.shape).copy_(torch.from_numpy(gw))
+        bucket.view(gw.size, gb.shape).copy_(torch.from_numpy(gb))
+        flat = bucket.all_reduce()
+        assert bucket.kind == "gloo"
+        assert torch.equal(flat[:gw.size].view(gw.shape), gw_t) and torch.equal(flat[gw.size:], gb_t)
         out[rank] = dict(lo=lo, hi=hi, y=y, gx=gx, gw=gw_t.numpy().copy(), gb=gb_t.numpy().copy())
     finally:
         dist.destroy_process_group()
