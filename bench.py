@@ -10,7 +10,8 @@ retained tokens), features and upstream gradients N(0,1), Kaiming-normal weights
 forward, input gradient, weight + bias gradient for all three keep rates on one batch
 (29 920 retained tokens per GPU).  Data are synthetic and seeded; there is no dataset behind
 this op.  With N > 1 every rank owns its own batch (weak scaling, sharded by clip) and the
-weight / bias gradients are all-reduced over NCCL every step, as data-parallel training does.
+weight / bias gradients are all-reduced every step, as data-parallel training does (bucket in
+symmetric memory, two-shot all-reduce over NVLink peer loads; NCCL where that is unavailable).
 
 Numbers on the JSON line
   value        tokens/s over all ranks with inputs already resident in HBM; every step reads a
@@ -215,7 +216,7 @@ def workload_config(n_gpus, note=None):
                     "Cin=Cout=192, 3x3, keep sweep {10,30,55}% by per-slice top-k",
         "tokens_per_step_per_gpu": sum(B * T * num_keep(r, H * W) for r in KEEPS),
         "keep_rates": list(KEEPS),
-        "parallelism": f"dp{n_gpus} (sharded by clip; NCCL all-reduce of weight/bias gradients)" if n_gpus > 1 else "single GPU",
+        "parallelism": f"dp{n_gpus} (sharded by clip; one all-reduce of the weight/bias gradient bucket per step)" if n_gpus > 1 else "single GPU",
         "l2": f"inputs larger than L2: every step reads a different one of {N_SETS} resident input sets (~{N_SETS * 47} MB > 126 MB)",
     }
     if note:

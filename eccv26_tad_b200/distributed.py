@@ -77,6 +77,12 @@ class GradBucket:
             except Exception as e:      # no peer access, handle exchange refused, op missing ...
                 self.fallback_reason = str(e)[:200]
                 self.buffer = None
+            # all ranks take the same path: one failure anywhere sends everybody to the fallback
+            ok = torch.tensor([1 if self.buffer is not None else 0], dtype=torch.int32, device=device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+            if int(ok.item()) == 0 and self.buffer is not None:
+                self.fallback_reason = "another rank could not set up symmetric memory"
+                self.buffer, self._symm_group = None, None
         if self.buffer is None:
             self.buffer = torch.zeros(numel, dtype=dtype, device=device)
             self.kind = "nccl" if device.type == "cuda" and world > 1 else ("gloo" if world > 1 else "none")
