@@ -10,8 +10,8 @@ retained tokens), features and upstream gradients N(0,1), Kaiming-normal weights
 forward, input gradient, weight + bias gradient for all three keep rates on one batch
 (29 920 retained tokens per GPU).  Data are synthetic and seeded; there is no dataset behind
 this op.  With N > 1 every rank owns its own batch (weak scaling, sharded by clip) and the
-weight / bias gradients are all-reduced every step, as data-parallel training does (bucket in
-symmetric memory, two-shot all-reduce over NVLink peer loads; NCCL where that is unavailable).
+weight / bias gradients are all-reduced over NCCL every step, as data-parallel training does
+(SVTAD_BENCH_ALLREDUCE=symm: bucket in symmetric memory, two-shot all-reduce over NVLink peer loads).
 
 Numbers on the JSON line
   value        tokens/s over all ranks with inputs already resident in HBM; every step reads a
@@ -292,11 +292,12 @@ def main():
     # the way DDP buckets the adapters' gradients (reference: src/eccv26_tad.py:288-300, 25 MB buckets)
     per_layer = KK * C * C + C
     n_grads = len(KEEPS) * per_layer
-    # N > 1: the bucket sits in symmetric memory and is summed by a two-shot all-reduce over NVLink peer loads
-    # (GradBucket falls back to NCCL where that cannot be set up; SVTAD_BENCH_ALLREDUCE=nccl forces NCCL)
+    # N > 1: NCCL all-reduce of the bucket.  SVTAD_BENCH_ALLREDUCE=symm puts the bucket in symmetric memory and
+    # sums it with a two-shot all-reduce over NVLink peer loads instead (measured 0.1714 vs 0.1914 ms per step on
+    # 8 GPUs); it stays opt-in because it has been run far less often than the NCCL path.
     from eccv26_tad_b200.distributed import GradBucket
     bucket = GradBucket(n_grads, torch.bfloat16, dev,
-                        allow_symmetric=os.environ.get("SVTAD_BENCH_ALLREDUCE", "symm") != "nccl")
+                        allow_symmetric=os.environ.get("SVTAD_BENCH_ALLREDUCE", "nccl") == "symm")
     grads, allreduce_kind = bucket.buffer, bucket.kind
     if world > 1 and bucket.kind == "nccl" and hasattr(bucket, "fallback_reason"):
         sys.stderr.write(f"[bench] symmetric-memory all-reduce unavailable ({bucket.fallback_reason}); using NCCL\n")
