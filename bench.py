@@ -232,6 +232,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying CUDA graphs")
+    ap.add_argument("--layer-streams", type=int, default=0, choices=[0, 1],
+                    help="1: the step's three layers (keep rates) run on three streams instead of one after the other")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-ref-cuda", action="store_true")
     ap.add_argument("--workload", default="sparseconv", choices=["sparseconv", "backbone"],
@@ -288,6 +290,7 @@ def main():
     n_max = max(it["n"] for it in host_sets[0])
     y_buf = torch.empty(n_max, C, dtype=torch.bfloat16, device=dev)
     gx_buf = torch.empty(n_max, C, dtype=torch.bfloat16, device=dev)
+    LAUNCHES_PER_LAYER = 4   # fwd, dgrad, wgrad partials (bias row included), reduce
     # one flat bucket for the gradients of the step's three layers (gw ++ gb each), all-reduced once per step
     # the way DDP buckets the adapters' gradients (reference: src/eccv26_tad.py:288-300, 25 MB buckets)
     per_layer = KK * C * C + C
@@ -306,7 +309,13 @@ def main():
     gw_buf, gb_buf = gw_bufs[0], gb_bufs[0]
     launches_per_step = 0
 
-    side = torch.cuda.Stream(device=dev)
+    # every layer (keep rate) has its own outputs and workspace, so the three layers of a step - which do not
+    # depend on one another - may run on streams of their own (--layer-streams 1)
+    y_bufs = [torch.empty(it["n"], C, dtype=torch.bfloat16, device=dev) for it in host_sets[0]]
+    gx_bufs = [torch.empty(it["n"], C, dtype=torch.bfloat16, device=dev) for it in host_sets[0]]
+    ws_l = [torch.empty(ws_bytes, dtype=torch.uint8, device=dev) for _ in KEEPS]
+    sides = [torch.cuda.Stream(device=dev) for _ in KEEPS]
+    lanes = [torch.cuda.Stream(device=dev) for _ in KEEPS]
 
     def raw_step(dk, stream=None, count=False):
         """One step through the C ABI on resident buffers: 3 keep rates x (fwd, then dgrad and wgrad+bias).
@@ -315,18 +324,25 @@ def main():
         cur = torch.cuda.current_stream()
         for li, it in enumerate(dk):
             n = it["n"]
+            main = lanes[li] if args.layer_streams else cur
+            side = sides[li]
+            if args.layer_streams:
+                main.wait_stream(cur)
             ops._lib.check(lib.svtad_conv_fwd(it["x"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(),
-                                              bias.data_ptr(), y_buf.data_ptr(), n, C, C, KK, 0, code, None, 0,
-                                              cur.cuda_stream))
-            side.wait_stream(cur)
+                                              bias.data_ptr(), y_bufs[li].data_ptr(), n, C, C, KK, 0, code, None, 0,
+                                              main.cuda_stream))
+            side.wait_stream(main)
             ops._lib.check(lib.svtad_conv_wgrad(it["gy"].data_ptr(), it["x"].data_ptr(), it["table"].data_ptr(),
                                                 gw_bufs[li].data_ptr(), gb_bufs[li].data_ptr(), n, C, C, KK, 0, code,
-                                                ws.data_ptr(), ws_bytes, side.cuda_stream))
+                                                ws_l[li].data_ptr(), ws_bytes, side.cuda_stream))
             ops._lib.check(lib.svtad_conv_dgrad(it["gy"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(),
-                                                gx_buf.data_ptr(), n, C, C, KK, 0, code, None, None, 0,
-                                                cur.cuda_stream))
-            cur.wait_stream(side)
-            nl += 4   # fwd, dgrad, wgrad partials (bias row included), reduce
+                                                gx_bufs[li].data_ptr(), n, C, C, KK, 0, code, None, None, 0,
+                                                main.cuda_stream))
+            main.wait_stream(side)
+            nl += LAUNCHES_PER_LAYER
+        if args.layer_streams:
+            for li in range(len(dk)):
+                cur.wait_stream(lanes[li])
         if world > 1:
             bucket.all_reduce()
         return nl

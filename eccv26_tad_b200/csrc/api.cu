@@ -168,8 +168,8 @@ extern "C" int svtad_conv_wgrad(const void* gy, const void* x, const int32_t* nb
         return SVTAD_OK;
     }
     SV_CHECK_ARG(gy && x && nbr, "svtad_conv_wgrad: null pointer");
-    SV_CHECK_ARG(aligned(gy, 16) && aligned(x, 16) && aligned(gw, 16) && aligned(nbr, 16),
-                 "svtad_conv_wgrad: gy, x, nbr and gw must be 16-byte aligned");
+    SV_CHECK_ARG(aligned(gy, 16) && aligned(x, 16) && aligned(gw, 16) && aligned(nbr, 16) && aligned(gb, 16),
+                 "svtad_conv_wgrad: gy, x, nbr, gw and gb must be 16-byte aligned");
     SV_CHECK_ARG(workspace != nullptr && aligned(workspace, 256), "svtad_conv_wgrad: workspace is null or not 256-byte aligned");
     if (use_tc(SVTAD_OP_WGRAD, n, cin, cout, kk, dtype))
         return tc_wgrad(gy, x, nbr, gw, gb, n, cin, cout, kk, tokens_per_batch, dtype, workspace, workspace_bytes, s);

@@ -70,7 +70,7 @@ int tc_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw, void* 
 size_t tc_wgrad_ws_bytes(int64_t n, int cin, int cout, int kk);
 int tc_read_error(int32_t* code_out);
 
-// the two tensor-core kernel families behind tc_* (conv_tc_hybrid.cu, conv_tc_gather4.cu)
+// the single-CTA tensor-core kernels behind tc_* (conv_tc_hybrid.cu)
 #define SV_DECLARE_TC_FAMILY(prefix)                                                                        \
     int prefix##_fwd(const ConvArgs& p, cudaStream_t s);                                                    \
     int prefix##_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s);                           \
@@ -78,7 +78,6 @@ int tc_read_error(int32_t* code_out);
                        int cin, int cout, int kk, int tpb, int dtype, void* ws, size_t ws_bytes,            \
                        cudaStream_t s);
 SV_DECLARE_TC_FAMILY(hybrid)
-SV_DECLARE_TC_FAMILY(gather4)
 // forward / dgrad on CTA pairs (conv_tc_pair.cu)
 int pair_fwd(const ConvArgs& p, cudaStream_t s);
 int pair_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s);

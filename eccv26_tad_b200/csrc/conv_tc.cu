@@ -1,10 +1,14 @@
 // Host side of the tcgen05 / TMEM SparseConv2D path: the device error word, tensor-map encoding, tile
-// and split planning, and the dispatch between the two kernel families
-//   conv_tc_hybrid.cu   (default)  gathered rows by per-warp cp.async, weight / gy tiles by TMA
-//   conv_tc_gather4.cu  (SVTAD_TC_IMPL=gather4)  everything by TMA, gathered rows with tile::gather4
-// Both replace opentad/models/bricks/implicit_gemm_v2.cu:197-417 (gather kernel + cuBLAS batched GEMM +
+// and split planning, and the dispatch between the kernel families
+//   conv_tc_hybrid.cu   one CTA per tile: gathered rows by per-warp cp.async, weight / gy tiles by TMA
+//   conv_tc_pair.cu     forward / dgrad on CTA pairs (cta_group::2) once row tiles outnumber the SMs
+// They replace opentad/models/bricks/implicit_gemm_v2.cu:197-417 (gather kernel + cuBLAS batched GEMM +
 // reduce kernel) and the atomic backward kernels opentad/models/bricks/2d_sparse_v3.cu:656-745.
 #include <cstdlib>
+#include <cstring>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "tc_common.cuh"
 
@@ -39,29 +43,32 @@ int tc_read_error(int32_t* code_out) {
     return SVTAD_OK;
 }
 
+// SM count of the current device (cached per device ordinal; a racing first call stores the same value)
 int tc_num_sms() {
-    static int cached = 0;
-    if (cached == 0) {
-        int dev = 0, v = 0;
-        if (cudaGetDevice(&dev) == cudaSuccess &&
-            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
-            cached = v;
-        else
-            cached = 148;
-    }
-    return cached;
+    constexpr int MAX_DEV = 64;
+    static int cached[MAX_DEV] = {0};
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev >= 0 && dev < MAX_DEV && cached[dev] > 0) return cached[dev];
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    if (dev >= 0 && dev < MAX_DEV) cached[dev] = v;
+    return v;
 }
 
-bool tc_pdl_enabled() {
-    // off by default: back-to-back launches gain 0.3-0.5 us each, but a step that forks wgrad onto a side
-    // stream got slower with it on B200 (0.187 vs 0.178 ms)
-    const char* e = getenv("SVTAD_PDL");
-    return e != nullptr && e[0] == '1';
-}
-
-bool tc_rotate_enabled() {
-    const char* e = getenv("SVTAD_TC_ROTATE");
-    return !(e != nullptr && e[0] == '0');
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device) instead of before every launch;
+// the value only ever grows
+int tc_ensure_smem(const void* kern, size_t bytes) {
+    static std::mutex mu;
+    static std::map<std::pair<const void*, int>, size_t> done;
+    int dev = 0;
+    SV_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> hold(mu);
+    auto key = std::make_pair(kern, dev);
+    auto it = done.find(key);
+    if (it != done.end() && it->second >= bytes) return SVTAD_OK;
+    SV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    done[key] = bytes;
+    return SVTAD_OK;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -86,6 +93,20 @@ int tc_make_map(CUtensorMap* map, int rank, const void* base, const uint64_t* di
 
 int tc_make_map_sw(CUtensorMap* map, int rank, const void* base, const uint64_t* dims, const uint32_t* box, int fp16,
                    int swizzle_bytes) {
+    // A descriptor depends only on (base, dims, box, element type, swizzle): a training step encodes the same few
+    // again and again, so the last ones are kept per thread.
+    struct Key { const void* base; uint64_t dims[3]; uint32_t box[3]; int rank, fp16, swz, dev; };
+    struct Slot { Key key; CUtensorMap map; bool used; };
+    constexpr int SLOTS = 32;
+    static thread_local Slot cache[SLOTS];
+    static thread_local unsigned next_slot = 0;
+    Key key;
+    memset(&key, 0, sizeof(key));
+    key.base = base; key.rank = rank; key.fp16 = fp16; key.swz = swizzle_bytes;
+    for (int i = 0; i < rank; ++i) { key.dims[i] = dims[i]; key.box[i] = box[i]; }
+    if (cudaGetDevice(&key.dev) != cudaSuccess) key.dev = -1;
+    for (int i = 0; i < SLOTS; ++i)
+        if (cache[i].used && memcmp(&cache[i].key, &key, sizeof(Key)) == 0) { *map = cache[i].map; return SVTAD_OK; }
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return set_error(SVTAD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
     // the driver call needs this thread to hold the device's context (autograd worker threads may not yet)
@@ -111,6 +132,8 @@ int tc_make_map_sw(CUtensorMap* map, int rank, const void* base, const uint64_t*
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return set_error(SVTAD_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    Slot& slot = cache[next_slot++ % SLOTS];
+    slot.key = key; slot.map = *map; slot.used = true;
     return SVTAD_OK;
 }
 
@@ -190,7 +213,6 @@ size_t tc_wgrad_ws_bytes(int64_t n, int cin, int cout, int kk) { return tc_wgrad
 __global__ void __launch_bounds__(256)
 wgrad_reduce4_kernel(const float* __restrict__ ws_w, int splits, const float* __restrict__ ws_b, int splits_b,
                      uint16_t* __restrict__ gw, uint16_t* __restrict__ gb, long n_w, int cout, int fp16) {
-    pdl_wait();
     long e = (blockIdx.x * (long)blockDim.x + threadIdx.x) * 4;
     const float* src;
     uint16_t* dst;
@@ -232,15 +254,10 @@ bool tc_supported(int op, int64_t n, int cin, int cout, int kk, int dtype) {
     return true;
 }
 
-static bool use_gather4() {
-    const char* e = getenv("SVTAD_TC_IMPL");
-    return e != nullptr && e[0] == 'g';
-}
-
 // Forward / dgrad on CTA pairs (tcgen05 cta_group::2) or on single CTAs.  Measured on B200 at C = 192: pairs win
 // once there are more row tiles than SMs (918-941 vs 820-850 TFLOP/s at 226 560 rows); below that one CTA
 // per (row tile, column block) starts sooner and uses narrower column blocks to fill the machine.
-// SVTAD_TC_IMPL=pair / hybrid / gather4 overrides the choice.
+// SVTAD_TC_IMPL=pair / hybrid overrides the choice.
 static bool use_pair(int64_t n) {
     const char* e = getenv("SVTAD_TC_IMPL");
     if (e != nullptr && *e) return e[0] == 'p';
@@ -250,18 +267,17 @@ static bool use_pair(int64_t n) {
 
 int tc_fwd(const ConvArgs& p, cudaStream_t s) {
     if (use_pair(p.n)) return pair_fwd(p, s);
-    return use_gather4() ? gather4_fwd(p, s) : hybrid_fwd(p, s);
+    return hybrid_fwd(p, s);
 }
 
 int tc_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s) {
     if (use_pair(p.n)) return pair_dgrad(p, status, s);
-    return use_gather4() ? gather4_dgrad(p, status, s) : hybrid_dgrad(p, status, s);
+    return hybrid_dgrad(p, status, s);
 }
 
 int tc_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw, void* gb, int64_t n, int cin, int cout,
              int kk, int tpb, int dtype, void* ws, size_t ws_bytes, cudaStream_t s) {
-    return use_gather4() ? gather4_wgrad(gy, x, nbr, gw, gb, n, cin, cout, kk, tpb, dtype, ws, ws_bytes, s)
-                         : hybrid_wgrad(gy, x, nbr, gw, gb, n, cin, cout, kk, tpb, dtype, ws, ws_bytes, s);
+    return hybrid_wgrad(gy, x, nbr, gw, gb, n, cin, cout, kk, tpb, dtype, ws, ws_bytes, s);
 }
 
 }  // namespace svtad

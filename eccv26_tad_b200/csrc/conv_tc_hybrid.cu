@@ -62,8 +62,6 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                    const int32_t* __restrict__ nbr, const uint16_t* __restrict__ bias,
                    uint16_t* __restrict__ out, const int32_t* __restrict__ status, long n, int cred, int cn,
                    int kk, int tpb, int nstage, int fp16, int m_tiles, int n_blks, int* __restrict__ err) {
-    pdl_wait();                 // nothing of global memory is touched before the predecessor has finished
-    pdl_launch_dependents();    // the next kernel in the stream may begin its own launch now
     if (DGRAD && status != nullptr && (__ldg(status) & SVTAD_TABLE_ASYMMETRIC)) return;
     constexpr int B_TILE_BYTES = b_tile_bytes_for(BN);
     constexpr int B_TX_BYTES = DGRAD ? BN * 128 : B_TILE_BYTES;
@@ -326,9 +324,7 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
                     const int32_t* __restrict__ nbr, float* __restrict__ ws_w, float* __restrict__ ws_b,
                     uint16_t* __restrict__ gw, uint16_t* __restrict__ gb,
                     long n, int cin, int cout, int kk, int tpb, long tokens_per_split, int n_nblk,
-                    int nstage, int fp16, int ones_block, int rotate, int* __restrict__ err) {
-    pdl_wait();
-    pdl_launch_dependents();
+                    int nstage, int fp16, int ones_block, int* __restrict__ err) {
     constexpr int B_TILE_BYTES = b_tile_bytes_for(BN);
     constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
     constexpr int TM_COLS = tmem_cols_for(BN);
@@ -358,7 +354,7 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
     int* my_rows = my_tab + 2 * tab_ints;              // [TILE_M] final gather rows of the current step
     // CTAs of different block pairs walk the token range from different starting points (see the
     // forward kernel); `src_stage` is the 64-token step that pipeline step `it` carries
-    const int rot = (rotate && total_stages > 0) ? (int)(((long)blockIdx.x * 5) % total_stages) : 0;
+    const int rot = total_stages > 0 ? (int)(((long)blockIdx.x * 5) % total_stages) : 0;
     auto src_stage = [&](int it) { int v = it + rot; return v >= total_stages ? v - total_stages : v; };
     // the step's table rows are contiguous in memory: copy them whole (16-byte cp.async, rows past the
     // end of this split read as zero bytes) one warp-iteration ahead; only these copies are committed
@@ -635,7 +631,7 @@ static int launch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaStre
     if (two) nstage &= ~1;
     const size_t smem = 1024 + nstage * stage + extra;
     auto kern = two ? conv_hybrid_kernel<BN, DGRAD, 2> : conv_hybrid_kernel<BN, DGRAD, 1>;
-    SV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    { int rc_s = tc_ensure_smem(reinterpret_cast<const void*>(kern), smem); if (rc_s) return rc_s; }
     const int m_tiles = (int)((p.n + TILE_M - 1) / TILE_M);
     const int n_blks = cn / BN;
     long tiles = (long)m_tiles * n_blks;
@@ -683,10 +679,9 @@ static int launch_wgrad_hybrid(const void* gy, const void* x, const int32_t* nbr
     const size_t smem = 1024 + nstage * stage + extra;
     const bool cluster = pl.cluster && (size_t)TILE_M * (BN + 4) * sizeof(float) <= nstage * stage;
     dim3 grid((unsigned)(pl.n_pairs * pl.n_nblk), (unsigned)pl.splits);
-    const int rot = tc_rotate_enabled() ? 1 : 0;
     if (cluster) {
         auto kern = wgrad_hybrid_kernel<BN, true>;
-        SV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        { int rc_s = tc_ensure_smem(reinterpret_cast<const void*>(kern), smem); if (rc_s) return rc_s; }
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(HY_THREADS);
@@ -701,14 +696,14 @@ static int launch_wgrad_hybrid(const void* gy, const void* x, const int32_t* nbr
         cfg.numAttrs = 1;
         SV_CUDA(cudaLaunchKernelEx(&cfg, kern, map_gy, (const uint16_t*)x, nbr, (float*)nullptr, (float*)nullptr,
                                    (uint16_t*)gw, (uint16_t*)gb, (long)n, cin, cout, kk, tpb, pl.tokens_per_split,
-                                   pl.n_nblk, nstage, fp16, pl.ones_block, rot, tc_error_ptr()));
+                                   pl.n_nblk, nstage, fp16, pl.ones_block, tc_error_ptr()));
         return SVTAD_OK;
     }
     auto kern = wgrad_hybrid_kernel<BN, false>;
-    SV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    { int rc_s = tc_ensure_smem(reinterpret_cast<const void*>(kern), smem); if (rc_s) return rc_s; }
     SV_CUDA(tc_launch(kern, grid, dim3(HY_THREADS), smem, s, map_gy, (const uint16_t*)x, nbr, ws_w, ws_b,
                       (uint16_t*)nullptr, (uint16_t*)nullptr, (long)n, cin, cout, kk, tpb, pl.tokens_per_split,
-                      pl.n_nblk, nstage, fp16, pl.ones_block, rot, tc_error_ptr()));
+                      pl.n_nblk, nstage, fp16, pl.ones_block, tc_error_ptr()));
     return SVTAD_OK;
 }
 

@@ -414,7 +414,7 @@ static int launch_conv_pair(const ConvArgs& p, const int32_t* status, cudaStream
         return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core conv (CTA pairs): not enough shared memory for BN=%d kk=%d", BN, p.kk);
     const size_t smem = 1024 + nstage * stage + extra;
     auto kern = conv_pair_kernel<BN, DGRAD>;
-    SV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    { int rc_s = tc_ensure_smem(reinterpret_cast<const void*>(kern), smem); if (rc_s) return rc_s; }
     const long m_tiles = (p.n + TILE_M - 1) / TILE_M;
     const int m_pairs = (int)((m_tiles + 1) / 2);
     const int n_blks = cn / BN;

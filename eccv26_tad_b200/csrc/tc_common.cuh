@@ -187,13 +187,6 @@ constexpr int tmem_cols_for(int bn) { return bn <= 32 ? 32 : bn <= 64 ? 64 : bn 
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, int x, int r0, int r1,
-                                            int r2, int r3, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-        ::"r"(dst), "l"(map), "r"(x), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(bar) : "memory");
-}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -234,14 +227,7 @@ struct alignas(16) TmaTail {   // 16-byte multiple: the table buffers behind it 
 constexpr int tmem_cols2_for(int bn) { return 2 * bn <= 64 ? 64 : 2 * bn <= 128 ? 128 : 2 * bn <= 256 ? 256 : 512; }
 
 
-// Programmatic dependent launch: a kernel launched with the attribute may start while its predecessor in
-// the stream is still draining; it must not touch global memory before pdl_wait().  Both are no-ops for
-// plain launches.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
 // ---- host helpers shared by the tensor-core translation units (defined in conv_tc.cu) ----
-bool tc_pdl_enabled();      // SVTAD_PDL=1 turns programmatic dependent launch on
 template <typename... KArgs, typename... Args>
 inline cudaError_t tc_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
     cudaLaunchConfig_t cfg = {};
@@ -249,16 +235,11 @@ inline cudaError_t tc_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = tc_pdl_enabled() ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 constexpr size_t TC_SMEM_LIMIT = 227 * 1024;
 int tc_num_sms();
-bool tc_rotate_enabled();   // SVTAD_TC_ROTATE=0 makes every CTA walk its K steps in the same order
+int tc_ensure_smem(const void* kern, size_t bytes);
 // 16-bit tensor map with 128-byte swizzle and zero fill outside the tensor; dims[0] is the contiguous one
 int tc_make_map(CUtensorMap* map, int rank, const void* base, const uint64_t* dims, const uint32_t* box, int fp16);
 // same with a 64- or 128-byte swizzle

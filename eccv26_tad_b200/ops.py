@@ -5,6 +5,7 @@ torch's caching allocator (so they are ordered on the current stream), picking t
 stream and device, and translating status codes to exceptions.
 """
 import torch
+from torch.utils.weak import WeakIdKeyDictionary
 
 from . import _lib
 
@@ -95,11 +96,32 @@ def _workspace(op, n, cin, cout, kk, code, device):
 
 
 # ----------------------------------------------------------------------------- table
+# Tables this module built itself are symmetric by construction (entry (i, k) = j  <=>  entry (j, KK-1-k) = i):
+# a full grid, a top-k subset of one, or a subset of a symmetric table.  They are remembered here (by tensor
+# object and version, weakly) so that the backward can use the gather form of the input gradient without the
+# device-side validation pass and without the scatter-form fallback launches.
+_symmetric = WeakIdKeyDictionary()
+
+
+def mark_symmetric(table):
+    """Declare ``table`` symmetric (valid until the tensor is written to)."""
+    _symmetric[table] = table._version
+    return table
+
+
+def is_known_symmetric(table):
+    """True for tables built by this module (or marked by the caller) and views of them, unmodified since."""
+    for t in (table, getattr(table, "_base", None)):
+        if t is not None and _symmetric.get(t) == t._version:
+            return True
+    return False
+
+
 def table_init(B, T, h, w, ksize=3, device="cuda"):
     out = torch.empty((B, T * h * w, ksize * ksize), dtype=torch.int32, device=device)
     with _on(out.device):
         _lib.check(_lib.load().svtad_table_init(B, T, h, w, ksize, _ptr(out), _stream()))
-    return out
+    return mark_symmetric(out)
 
 
 def table_build(scores, k_keep, h, w, ksize=3):
@@ -114,7 +136,7 @@ def table_build(scores, k_keep, h, w, ksize=3):
     with _on(scores.device):
         _lib.check(_lib.load().svtad_table_build(_ptr(scores), n_seg, seg_len, k_keep, h, w, ksize,
                                                  _ptr(kept), _ptr(table), _stream()))
-    return kept, table
+    return kept, mark_symmetric(table)
 
 
 def topk_select(scores, k_keep):
@@ -133,6 +155,7 @@ def topk_select(scores, k_keep):
 def table_remap(table, idx, scratch=None):
     """table int32 [B, N_prev, KK], idx int64 [B, N_new] -> int32 [B, N_new, KK]."""
     _require_cuda(table, idx)
+    sym = is_known_symmetric(table)
     table = _i32_table(table)
     idx = idx.to(torch.int64).contiguous()
     B, n_prev, kk = table.shape
@@ -143,7 +166,7 @@ def table_remap(table, idx, scratch=None):
     with _on(table.device):
         _lib.check(_lib.load().svtad_table_remap(_ptr(table), _ptr(idx), B, n_prev, n_new, kk,
                                                  _ptr(scratch), _ptr(out), _stream()))
-    return out
+    return mark_symmetric(out) if sym else out
 
 
 def table_select_remap(scores, table, k_keep):
@@ -153,6 +176,7 @@ def table_select_remap(scores, table, k_keep):
     if scores.dtype != torch.float32:
         scores = scores.float()
     scores = scores.contiguous()
+    sym = is_known_symmetric(table)
     table = _i32_table(table)
     B, n_prev, kk = table.shape
     if tuple(scores.shape) != (B, n_prev):
@@ -163,7 +187,7 @@ def table_select_remap(scores, table, k_keep):
     with _on(table.device):
         _lib.check(_lib.load().svtad_table_select_remap(_ptr(scores), _ptr(table), B, n_prev, k_keep, kk, _ptr(kept),
                                                         _ptr(idx), _ptr(out), _stream()))
-    return idx, out
+    return idx, (mark_symmetric(out) if sym else out)
 
 
 def table_check(nbr, tokens_per_batch=0, status=None):
@@ -209,6 +233,7 @@ def conv_dgrad(gy, nbr, weight, tokens_per_batch=0, table_status=None, assume_sy
     kk, cin, cout = weight.shape
     gy = _c16(gy)
     weight = _c16(weight)
+    assume_symmetric = assume_symmetric or (table_status is None and is_known_symmetric(nbr))
     nbr = _i32_table(nbr)
     n = gy.numel() // cout
     if weight.dtype != gy.dtype:
@@ -249,16 +274,19 @@ def conv_wgrad(gy, x, nbr, kk, tokens_per_batch=0, with_bias=True):
     return gw, gb
 
 
-def conv_bwd(gy, x, nbr, weight, tokens_per_batch=0, table_status=None, need_x=True, need_w=True, need_b=True):
+def conv_bwd(gy, x, nbr, weight, tokens_per_batch=0, table_status=None, need_x=True, need_w=True, need_b=True,
+             assume_symmetric=False):
     """Both gradients of one layer in one library call (the weight gradient runs next to the input gradient
     on a stream of the library; for the caller everything is ordered on the current stream).
-    Returns ``(gx, gw, gb)`` with None for what was not asked for."""
+    ``assume_symmetric=True`` (or a table this module built itself) skips the device-side table validation and
+    the scatter-form fallback of the input gradient.  Returns ``(gx, gw, gb)`` with None for what was not asked for."""
     _require_cuda(gy, x, nbr, weight)
     code = _dtype_code(gy)
     kk, cin, cout = weight.shape
     gy = _c16(gy)
     x = _c16(x)
     weight = _c16(weight)
+    assume_symmetric = assume_symmetric or (table_status is None and is_known_symmetric(nbr))
     nbr = _i32_table(nbr)
     n = gy.numel() // cout
     if weight.dtype != gy.dtype or x.dtype != gy.dtype:
@@ -270,13 +298,19 @@ def conv_bwd(gy, x, nbr, weight, tokens_per_batch=0, table_status=None, need_x=T
     gw = torch.empty((kk, cin, cout), dtype=gy.dtype, device=dev) if need_w else None
     gb = torch.empty((cout,), dtype=gy.dtype, device=dev) if need_b else None
     with _on(dev):
-        if need_x and table_status is None:
+        if assume_symmetric:
+            table_status = None
+        elif need_x and table_status is None:
             table_status = table_check(nbr, tokens_per_batch)
-        op = _lib.OP_BWD if (need_x and need_w) else (_lib.OP_WGRAD if need_w else _lib.OP_DGRAD)
-        ws, ws_bytes = _workspace(op, n, cin, cout, kk, code, dev)
+        if assume_symmetric:     # no scatter-form part in the workspace
+            op = _lib.OP_WGRAD if need_w else None
+        else:
+            op = _lib.OP_BWD if (need_x and need_w) else (_lib.OP_WGRAD if need_w else _lib.OP_DGRAD)
+        ws, ws_bytes = _workspace(op, n, cin, cout, kk, code, dev) if op is not None else (None, 0)
         _lib.check(_lib.load().svtad_conv_bwd(_ptr(gy), _ptr(x), _ptr(nbr), _ptr(weight), _ptr(gx), _ptr(gw), _ptr(gb),
                                               n, cin, cout, kk, tokens_per_batch, code,
-                                              _ptr(table_status) if need_x else None, _ptr(ws), ws_bytes, _stream()))
+                                              _ptr(table_status) if (need_x and not assume_symmetric) else None,
+                                              _ptr(ws), ws_bytes, _stream()))
     return gx, gw, gb
 
 
@@ -297,6 +331,12 @@ def conv_wgrad_static(gy, x, nbr, gw, gb, tokens_per_batch=0):
     if nbr.dtype != torch.int32 or gy.dtype != x.dtype or gw.dtype != x.dtype:
         raise ValueError("conv_wgrad_static: nbr must be int32 and gy, x, gw must share one dtype")
     n = x.numel() // cin
+    _check_shapes("conv_wgrad_static", n, kk, nbr, x=(x, cin), grad_output=(gy, cout))
+    if gb is not None and (gb.numel() != cout or gb.dtype != x.dtype):
+        raise ValueError(f"conv_wgrad_static: gb must hold {cout} elements of x's dtype")
+    for t in (gy, x, nbr, gw) + ((gb,) if gb is not None else ()):
+        if t.numel() and t.data_ptr() % 16:
+            raise ValueError("conv_wgrad_static needs 16-byte aligned tensors (it cannot make copies)")
     with _on(x.device):
         _lib.check(_lib.load().svtad_conv_wgrad_static(_ptr(gy), _ptr(x), _ptr(nbr), _ptr(gw), _ptr(gb), n, cin,
                                                        cout, kk, tokens_per_batch, code, _stream()))

@@ -60,8 +60,23 @@ class _PerTableCache:
 _table_cache = _PerTableCache()
 
 
+_SYMMETRIC = "symmetric by construction"
+
+
 def _status_for(nbr, tokens_per_batch):
+    """What the backward needs to know about a table: ``_SYMMETRIC`` for tables built by this package (no
+    validation pass, no scatter-form fallback), else the device status word of ``svtad_table_check``."""
+    if tokens_per_batch == 0 and ops.is_known_symmetric(nbr):
+        return _SYMMETRIC
     return _table_cache.get(nbr, ("status", tokens_per_batch), lambda: ops.table_check(nbr, tokens_per_batch))
+
+
+def _bwd(grad_output, x, nbr, weight, tpb, status, need_x, need_w, need_b):
+    if status is _SYMMETRIC:
+        return ops.conv_bwd(grad_output, x, nbr, weight, tpb, need_x=need_x, need_w=need_w, need_b=need_b,
+                            assume_symmetric=True)
+    return ops.conv_bwd(grad_output, x, nbr, weight, tpb, table_status=status, need_x=need_x, need_w=need_w,
+                        need_b=need_b)
 
 
 class SparseConv2dFunction(Function):
@@ -104,9 +119,8 @@ class SparseConv2dFunction(Function):
                 status = _status_for(neighbor_indices, tpb)
         # one library call: the two halves of the backward are independent, so the weight gradient runs
         # next to the input gradient (the reference launches them one after the other, :100-117)
-        grad_input, grad_weight, grad_bias = ops.conv_bwd(grad_output, x.reshape(-1, ctx.C_in), nbr, weight, tpb,
-                                                          table_status=status, need_x=need_x, need_w=need_w,
-                                                          need_b=need_b)
+        grad_input, grad_weight, grad_bias = _bwd(grad_output, x.reshape(-1, ctx.C_in), nbr, weight, tpb, status,
+                                                  need_x, need_w, need_b)
         if grad_input is not None and x.dim() == 3:
             grad_input = grad_input.view(x.shape)
         if not need_w:
@@ -144,8 +158,8 @@ class _SparseConv2dCastFunction(Function):
         status = None
         if need_x:
             status = ctx.table_status if ctx.table_status is not None else _status_for(neighbor_indices, tpb)
-        gx, gw, gb = ops.conv_bwd(grad_output, x.reshape(-1, ctx.C_in), neighbor_indices.reshape(-1, kk), weight_c, tpb,
-                                  table_status=status, need_x=need_x, need_w=need_w, need_b=need_b)
+        gx, gw, gb = _bwd(grad_output, x.reshape(-1, ctx.C_in), neighbor_indices.reshape(-1, kk), weight_c, tpb,
+                          status, need_x, need_w, need_b)
         if gx is not None and x.dim() == 3:
             gx = gx.view(x.shape)
         gw = gw.to(ctx.param_dtype) if (need_w and gw is not None) else None
@@ -204,6 +218,8 @@ class SparseConv2d(nn.Module):
         table = neighbor_indices
         if table.dtype != torch.int32:
             table = _table_cache.get(neighbor_indices, "int32", lambda: neighbor_indices.to(torch.int32))
+            if ops.is_known_symmetric(neighbor_indices):
+                ops.mark_symmetric(table)
         if table.dim() == 3:
             table = _table_cache.get(table, "flat", lambda: table.reshape(-1, kk)) if table.is_contiguous() \
                 else table.reshape(-1, kk)
@@ -226,8 +242,22 @@ class SparseConv2d(nn.Module):
             output = output.view(B, N, -1)
         return output
 
+    def invalidate_cast_cache(self):
+        """Drops the cached low-precision parameter copies.  They are keyed on the parameters' version counters,
+        which in-place tensor ops bump; writes that bypass them (``param.data`` arithmetic of some fused
+        optimizers, raw-pointer updates) do not, so such code must call this after every update - or set
+        ``module.cache_casts = False`` to cast on every call as the reference does (:196-203)."""
+        self._cast_cache = None
+
+    def train(self, mode=True):
+        self._cast_cache = None
+        return super().train(mode)
+
     def _cast_params(self, dtype):
         w, b = self.weight, self.bias
+        if not getattr(self, "cache_casts", True):
+            with torch.no_grad():
+                return w.detach().to(dtype), None if b is None else b.detach().to(dtype)
         key = (dtype, w.data_ptr(), w._version, None if b is None else (b.data_ptr(), b._version))
         cached = getattr(self, "_cast_cache", None)
         if cached is None or cached[0] != key:
@@ -244,6 +274,7 @@ class SparseConv2d(nn.Module):
         if w is not None and w.dim() == 3 and w.shape != self.weight.shape and \
                 w.permute(1, 0, 2).shape == self.weight.shape:
             state_dict[key] = w.permute(1, 0, 2).contiguous()
+        self._cast_cache = None
         super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
 
     def extra_repr(self):

@@ -29,6 +29,9 @@ def lib():
         if not os.path.exists(_LIB_PATH):
             build()
         _lib = ctypes.CDLL(_LIB_PATH)
+        if _lib.svtad_oracle_version() < 3:      # an older build is lying around: rebuild and reload
+            build(force=True)
+            _lib = ctypes.CDLL(_LIB_PATH)
     return _lib
 
 
@@ -51,9 +54,14 @@ def _acc(acc):
 
 
 def fwd(x, nbr, w, bias=None, tokens_per_batch=0, acc="f64"):
+    """``nbr`` may hold fewer rows than ``x`` (a sample of the table's rows, ``tokens_per_batch == 0`` only):
+    the result then has one row per table row given."""
     x, w = _f32(x), _f32(w)
     nbr = np.ascontiguousarray(nbr, dtype=np.int32)
     n, cin = x.shape
+    if nbr.shape[0] != n:
+        assert tokens_per_batch == 0 and nbr.shape[0] < n, "a row sample needs global indices"
+        n = nbr.shape[0]
     kk, _, cout = w.shape
     b = _f32(bias) if bias is not None else None
     y = np.empty((n, cout), dtype=_acc(acc))
@@ -72,6 +80,21 @@ def dgrad(gy, nbr, w, tokens_per_batch=0, acc="f64"):
     getattr(lib(), "svtad_oracle_dgrad_" + acc)(
         _ptr(gy), _ptr(nbr), _ptr(w), _ptr(gx),
         ctypes.c_int64(n), cin, cout, kk, int(tokens_per_batch))
+    return gx
+
+
+def dgrad_rows(gy, nbr, w, rows, tokens_per_batch=0):
+    """Rows ``rows`` of ``dgrad(gy, nbr, w)`` (float64), without computing the others."""
+    gy, w = _f32(gy), _f32(w)
+    nbr = np.ascontiguousarray(nbr, dtype=np.int32)
+    sel = np.ascontiguousarray(rows, dtype=np.int64)
+    n, cout = gy.shape
+    kk, cin, _ = w.shape
+    assert sel.size == 0 or (sel.min() >= 0 and sel.max() < n)
+    assert len(np.unique(sel)) == sel.size
+    gx = np.empty((sel.size, cin), dtype=np.float64)
+    lib().svtad_oracle_dgrad_rows_f64(_ptr(gy), _ptr(nbr), _ptr(w), _ptr(gx), _ptr(sel), ctypes.c_int64(sel.size),
+                                      ctypes.c_int64(n), cin, cout, kk, int(tokens_per_batch))
     return gx
 
 

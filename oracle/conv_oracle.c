@@ -162,7 +162,56 @@ static inline int64_t sv_off(int64_t i, int tpb) { return tpb > 0 ? (i / tpb) * 
 DEFINE_ORACLE(f32, float)
 DEFINE_ORACLE(f64, double)
 
-int svtad_oracle_version(void) { return 2; }
+
+/*
+ * Row-subset flavour of the input gradient (double accumulate): gx_sel[r,:] = gx[sel[r],:] for the
+ * `nsel` target rows listed in `sel`, computed from the same scatter-form definition as above
+ * (2d_sparse_v3.cu:679-707) without evaluating the other rows.  Lets full-size problems be checked
+ * on a sample of their rows in seconds.
+ */
+SV_CLONES void svtad_oracle_dgrad_rows_f64(const float* gy, const int32_t* nbr, const float* w, double* gx_sel,
+                                           const int64_t* sel, int64_t nsel, int64_t n, int cin, int cout,
+                                           int kk, int tpb) {
+    /* position of every selected target row in `sel`, -1 for the rest */
+    int64_t* pos = (int64_t*)malloc(sizeof(int64_t) * (size_t)(n ? n : 1));
+    for (int64_t j = 0; j < n; ++j) pos[j] = -1;
+    for (int64_t r = 0; r < nsel; ++r) pos[sel[r]] = r;
+    int64_t* start = (int64_t*)calloc((size_t)nsel + 1, sizeof(int64_t));
+    for (int64_t i = 0; i < n; ++i)
+        for (int k = 0; k < kk; ++k) {
+            int32_t j = nbr[i * kk + k];
+            if (j != -1 && pos[j + sv_off(i, tpb)] >= 0) start[pos[j + sv_off(i, tpb)] + 1]++;
+        }
+    for (int64_t r = 0; r < nsel; ++r) start[r + 1] += start[r];
+    int64_t nnz = start[nsel];
+    int64_t* fill = (int64_t*)malloc(sizeof(int64_t) * ((size_t)nsel + 1));
+    memcpy(fill, start, sizeof(int64_t) * ((size_t)nsel + 1));
+    int64_t* src = (int64_t*)malloc(sizeof(int64_t) * (size_t)(nnz ? nnz : 1));
+    for (int64_t i = 0; i < n; ++i)
+        for (int k = 0; k < kk; ++k) {
+            int32_t j = nbr[i * kk + k];
+            if (j != -1 && pos[j + sv_off(i, tpb)] >= 0) src[fill[pos[j + sv_off(i, tpb)]]++] = i * kk + k;
+        }
+    _Pragma("omp parallel for schedule(dynamic, 4)")
+    for (int64_t r = 0; r < nsel; ++r) {
+        double* out = gx_sel + r * (int64_t)cin;
+        for (int ci = 0; ci < cin; ++ci) out[ci] = 0.0;
+        for (int64_t e = start[r]; e < start[r + 1]; ++e) {
+            int64_t i = src[e] / kk;
+            int k = (int)(src[e] % kk);
+            const float* g = gy + i * (int64_t)cout;
+            for (int ci = 0; ci < cin; ++ci) {
+                const float* wr = w + ((int64_t)k * cin + ci) * cout;
+                double s = 0.0;
+                for (int co = 0; co < cout; ++co) s += (double)g[co] * (double)wr[co];
+                out[ci] += s;
+            }
+        }
+    }
+    free(pos); free(start); free(fill); free(src);
+}
+
+int svtad_oracle_version(void) { return 3; }
 
 /* Number of OpenMP threads the timed functions use (launchers such as torchrun export OMP_NUM_THREADS=1). */
 #ifdef _OPENMP

@@ -193,8 +193,11 @@ if __name__ == "__main__":
     import sys
     sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("SVTAD_REFERENCE_ROOT"),
+                    help="root of the reference checkout (default: $SVTAD_REFERENCE_ROOT)")
     a = ap.parse_args()
+    if not a.reference:
+        ap.error("give --reference or set SVTAD_REFERENCE_ROOT")
     make_table_fixtures(a.reference)
     make_conv_fixtures()
     for f in sorted(os.listdir(HERE)):

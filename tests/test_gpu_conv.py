@@ -181,6 +181,78 @@ def test_config3_large_channels_reduced_rows(C, ks):
     _check_all(table, x, w, b, gy, outs, 2e-2)
 
 
+def _check_sampled(table, x, w, b, gy, outs, tol, row_step=64, n_ci=8):
+    """Full-size problems against the float64 oracle on a sample: every ``row_step``-th row of the forward output
+    and of the input gradient, ``n_ci`` input channels of the weight gradient (all taps, all output channels), the
+    whole bias gradient.  Each error is max|a - ref| / max|ref| over the sampled entries."""
+    y, gx, gw, gb = outs
+    tn = table.numpy()
+    n, kk = tn.shape
+    sel = np.arange(row_step // 2, n, row_step)
+    xf, wf, bf, gf = (f32np(t) for t in (x, w, b, gy))
+    cs = np.linspace(0, x.shape[1] - 1, n_ci).astype(np.int64)
+    egw, _ = oconv.wgrad(gf, np.ascontiguousarray(xf[:, cs]), tn, kk, with_bias=False)
+    errs = {
+        "y": oconv.rel_err(f32np(y)[sel], oconv.fwd(xf, tn[sel], wf, bf)),
+        "gx": oconv.rel_err(f32np(gx)[sel], oconv.dgrad_rows(gf, tn, wf, sel)),
+        "gw": oconv.rel_err(f32np(gw)[:, cs], egw),
+        "gb": oconv.rel_err(f32np(gb), gf.astype(np.float64).sum(0)),
+    }
+    for k, v in errs.items():
+        assert v < tol, f"{k}: rel err {v:.3e} >= {tol}"
+    return errs
+
+
+@pytest.mark.parametrize("C,ks", [(256, 3), (256, 5), (768, 3), (768, 5), (1024, 3), (1024, 5)])
+def test_config3_full_size_against_sampled_oracle(C, ks):
+    """The large-channel configuration at its configured size (batch 4, T=80, keep 30 % = 18 880 rows; C in
+    {256, 768, 1024}; 3x3 and 5x5) through the default dispatch, checked against the float64 oracle on a sample
+    of rows / channels so that the CPU side finishes in seconds."""
+    _, _, table = make_table(4, 80, 14, 14, 0.3, ks, BASE_SEED + 3)
+    n = table.shape[0]
+    assert n == 18880
+    x, w, b, gy = make_conv_inputs(n, C, C, ks, torch.bfloat16, BASE_SEED + 3, bias="random")
+    assert _ops().path_for(0, n, C, C, ks * ks, torch.bfloat16) == "tc"
+    outs = _run_all(table, x, w, b, gy)
+    _check_sampled(table, x, w, b, gy, outs, 2e-2, row_step=32, n_ci=8)
+
+
+def _chain_table(n):
+    table = -np.ones((n, 9), dtype=np.int32)
+    table[:, 4] = np.arange(n)
+    table[1:, 3] = np.arange(n - 1)
+    table[:-1, 5] = np.arange(1, n)
+    return torch.from_numpy(table)
+
+
+@pytest.mark.parametrize("n", [148 * 128, 148 * 128 + 1])
+def test_default_dispatch_on_both_sides_of_the_pair_switch(n):
+    """With no override the forward / dgrad run on single CTAs while the row tiles do not outnumber the SMs (148
+    tiles of 128 rows on a B200) and on CTA pairs from one tile more; both sides against the oracle."""
+    assert "SVTAD_TC_IMPL" not in os.environ
+    table = _chain_table(n)
+    x, w, b, gy = make_conv_inputs(n, 192, 192, 3, torch.bfloat16, n % 1000, bias="random")
+    outs = _run_all(table, x, w, b, gy)
+    _check_sampled(table, x, w, b, gy, outs, 2e-2, row_step=16, n_ci=16)
+    # the last rows (a one-row tile on the far side of the switch) in full
+    tail = np.arange(n - 130, n)
+    tn = table.numpy()
+    xf, wf, bf, gf = (f32np(t) for t in (x, w, b, gy))
+    assert oconv.rel_err(f32np(outs[0])[tail], oconv.fwd(xf, tn[tail], wf, bf)) < 2e-2
+    assert oconv.rel_err(f32np(outs[1])[tail], oconv.dgrad_rows(gf, tn, wf, tail)) < 2e-2
+
+
+def test_geometric_tables_on_both_sides_of_the_pair_switch():
+    """Same with tables from the builder: 18 880 rows (148 row tiles, single CTAs) and 19 520 rows (153 tiles, pairs)."""
+    for keep, rows in ((0.30, 18880), (0.31, 19520)):
+        _, _, table = make_table(4, 80, 14, 14, keep, 3, 41)
+        n = table.shape[0]
+        assert n == rows
+        x, w, b, gy = make_conv_inputs(n, 192, 192, 3, torch.bfloat16, 41, bias="random")
+        outs = _run_all(table, x, w, b, gy)
+        _check_sampled(table, x, w, b, gy, outs, 2e-2, row_step=32, n_ci=8)
+
+
 def test_config3_full_size_adjoint_identities():
     """Full size (batch 4, T=80, keep 30%, C=256): <fwd(x), gy> == <x, dgrad(gy)> == <W, wgrad>."""
     ops = _ops()

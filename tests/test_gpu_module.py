@@ -153,3 +153,54 @@ def test_kernel_size_5_module():
     assert oconv.rel_err(f32np(y), ey) < 2e-2
     assert oconv.rel_err(f32np(xc.grad), egx) < 2e-2
     assert oconv.rel_err(f32np(m.weight.grad), egw) < 2e-2
+
+
+def test_reference_wrapper_runs_unchanged_on_top_of_the_shim():
+    """The reference's own ``sparse_conv_layer.py`` (byte-compiled by ``oracle/build_ref.py`` into ``oracle/_ref``;
+    its ``import opentad_sparse_ops`` answered by this package's module) - ITS SparseConv2d / SparseConv2dFunction,
+    forward and backward under bf16 autocast with fp32 master parameters, 2-D and batched 3-D input, and in plain
+    fp32 - against the oracle."""
+    from oracle import build_ref
+    from eccv26_tad_b200 import opentad_sparse_ops as shim
+    ref = build_ref.load_wrapper(shim)
+    if ref is None:
+        pytest.skip("oracle/_ref/ref_sparse_conv_layer.pyc has not been built")
+    assert ref.sparse_lib_opt is shim                     # no JIT fallback to the reference's CUDA sources
+    _, _, tab1 = make_table(1, 6, 14, 14, 0.3, 3, 71)
+    N = tab1.shape[0]
+    B = 2
+    glob = torch.cat([torch.where(tab1 >= 0, tab1 + i * N, tab1) for i in range(B)])
+    x, w, b, gy = make_conv_inputs(B * N, 192, 192, 3, torch.float32, 71, bias="random")
+    m = ref.SparseConv2d(192, 192).cuda()
+    assert tuple(m.weight.shape) == (9, 192, 192)
+    with torch.no_grad():
+        m.weight.copy_(w); m.bias.copy_(b)
+    xb, wb, bb, gb_ = (t.bfloat16() for t in (x, w, b, gy))
+    ey, egx, egw, egb = _oracle_grads(glob, xb, wb, bb, gb_)
+    cases = [(x.cuda(), glob.cuda(), gy.cuda().bfloat16()),                                     # [N, C], global indices
+             (x.view(B, N, 192).cuda(), tab1.unsqueeze(0).repeat(B, 1, 1).cuda().long(),        # [B, N, C], local, int64
+              gy.view(B, N, 192).cuda().bfloat16())]
+    for xin, table, g in cases:
+        m.zero_grad()
+        xc = xin.clone().requires_grad_(True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = m(xc, table)
+        assert y.dtype == torch.bfloat16 and y.shape[:-1] == xin.shape[:-1]
+        y.backward(g)
+        assert oconv.rel_err(f32np(y).reshape(-1, 192), ey) < 2e-2
+        assert oconv.rel_err(f32np(xc.grad).reshape(-1, 192), egx) < 2e-2
+        assert oconv.rel_err(f32np(m.weight.grad), egw) < 2e-2
+        assert oconv.rel_err(f32np(m.bias.grad), egb) < 2e-2
+    # fp32, small-channel branch of the reference wrapper (fwd + bias added by the wrapper, :86-87)
+    x, w, b, gy = make_conv_inputs(N, 64, 64, 3, torch.float32, 72, bias="random")
+    m = ref.SparseConv2d(64, 64).cuda()
+    with torch.no_grad():
+        m.weight.copy_(w); m.bias.copy_(b)
+    xc = x.cuda().requires_grad_(True)
+    y = m(xc, tab1.cuda())
+    y.backward(gy.cuda())
+    ey, egx, egw, egb = _oracle_grads(tab1, x, w, b, gy)
+    assert oconv.rel_err(f32np(y), ey) < 1e-5 and oconv.rel_err(f32np(xc.grad), egx) < 1e-5
+    assert oconv.rel_err(f32np(m.weight.grad), egw) < 1e-5 and oconv.rel_err(f32np(m.bias.grad), egb) < 1e-5
+    from eccv26_tad_b200 import ops
+    assert ops.device_error() == 0

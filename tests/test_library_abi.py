@@ -46,6 +46,9 @@ def test_host_side_validation_returns_codes():
     assert rc == _lib.ERR_ARG and "null" in _lib.last_error()
     rc = lib.svtad_conv_wgrad(None, None, None, None, None, 4, 8, 8, 9, 0, _lib.F32, None, 0, None)
     assert rc == _lib.ERR_ARG
+    # a bias-gradient pointer at an odd offset is refused before any launch (the kernels store 8 bytes at a time)
+    rc = lib.svtad_conv_wgrad(256, 256, 256, 256, 256 + 6, 4, 8, 8, 9, 0, _lib.BF16, 256, 1 << 20, None)
+    assert rc == _lib.ERR_ARG and "gb" in _lib.last_error()
     rc = lib.svtad_table_build(None, 4, 196, 300, 14, 14, 3, None, None, None)
     assert rc == _lib.ERR_ARG and "k_keep" in _lib.last_error()
     rc = lib.svtad_table_build(None, 4, 200, 20, 14, 14, 3, None, None, None)
@@ -115,6 +118,43 @@ def test_shape_mismatches_raise_before_any_launch():
     ops._check_shapes("conv_wgrad", 5, 9, nbr, grad_output=(torch.zeros(5, 8), 8))
 
 
+def test_static_wgrad_wrapper_checks_shapes_before_the_library_sees_them():
+    """conv_wgrad_static cannot copy or allocate, so every mismatch must be refused on the host."""
+    import torch
+    from eccv26_tad_b200 import ops
+
+    class FakeCuda(torch.Tensor):          # CPU storage that claims to live on the device: nothing is launched
+        is_cuda = True
+
+    def t(*shape, dtype=torch.bfloat16):
+        return torch.zeros(*shape, dtype=dtype).as_subclass(FakeCuda)
+
+    n, c = 64, 8
+    gw, gb = t(9, c, c), t(c)
+    nbr = t(n, 9, dtype=torch.int32)
+    with pytest.raises(ValueError, match="grad_output"):
+        ops.conv_wgrad_static(t(n - 1, c), t(n, c), nbr, gw, gb)
+    with pytest.raises(ValueError, match="neighbor table"):
+        ops.conv_wgrad_static(t(n, c), t(n, c), t(n - 2, 9, dtype=torch.int32), gw, gb)
+    with pytest.raises(ValueError, match="gb must hold"):
+        ops.conv_wgrad_static(t(n, c), t(n, c), nbr, gw, t(c + 1))
+    with pytest.raises(ValueError, match="gb must hold"):
+        ops.conv_wgrad_static(t(n, c), t(n, c), nbr, gw, t(c, dtype=torch.float32))
+    with pytest.raises(ValueError, match="16-byte aligned"):
+        ops.conv_wgrad_static(t(n, c), t(n, c), nbr, gw, t(c + 3)[3:])
+
+
+def test_tables_built_by_the_package_are_tagged_symmetric():
+    import torch
+    from eccv26_tad_b200 import ops
+    a = torch.zeros(4, 9, dtype=torch.int32)
+    assert not ops.is_known_symmetric(a)
+    ops.mark_symmetric(a)
+    assert ops.is_known_symmetric(a) and ops.is_known_symmetric(a.view(2, 2, 9))
+    a[0, 0] = 1                                       # written to: the tag no longer holds
+    assert not ops.is_known_symmetric(a)
+
+
 def test_legacy_checkpoint_layout_is_remapped_on_load():
     """Weights stored as (C_in, 9, C_out) load into the (9, C_in, C_out) parameter, as with the reference's
     remap_legacy_sparse_conv_weights (opentad/utils/checkpoint.py:44-57)."""
@@ -139,3 +179,20 @@ def test_legacy_checkpoint_layout_is_remapped_on_load():
     dst2 = Adapter()
     dst2.load_state_dict(src.state_dict())
     assert torch.equal(dst2.sparse_conv.weight, src.sparse_conv.weight)
+
+
+def test_reference_wrapper_binds_to_the_shim_when_built():
+    """Where ``oracle/_ref`` holds the byte-compiled reference wrapper, executing it with this package's
+    ``opentad_sparse_ops`` in place picks the shim up (no JIT build of the reference's CUDA sources) and exposes
+    the reference's class with the reference's constructor signature."""
+    import inspect
+    from oracle import build_ref
+    from eccv26_tad_b200 import SparseConv2d, opentad_sparse_ops as shim
+    ref = build_ref.load_wrapper(shim)
+    if ref is None:
+        pytest.skip("oracle/_ref/ref_sparse_conv_layer.pyc has not been built")
+    assert ref.sparse_lib_opt is shim
+    theirs = list(inspect.signature(ref.SparseConv2d.__init__).parameters)
+    ours = list(inspect.signature(SparseConv2d.__init__).parameters)
+    assert ours[:len(theirs)] == theirs
+    assert list(ref.SparseConv2d(8, 12).state_dict()) == list(SparseConv2d(8, 12).state_dict())

@@ -77,3 +77,26 @@ def test_asymmetric_table_and_empty():
     gw, _ = oconv.wgrad(gy, x, tab, kk)
     assert abs((gw * wt).sum() - lhs) < 1e-9 * max(1, abs(lhs))
     assert oconv.fwd(x[:0], tab[:0], wt).shape == (0, cout)
+
+
+def test_row_and_channel_samples_equal_the_full_oracle():
+    """The sampled forms used on full-size problems (forward rows, input-gradient rows, weight gradient of a
+    few input channels) give exactly the corresponding entries of the full computation."""
+    rng = np.random.default_rng(6)
+    scores = rng.standard_normal((6, 196)).astype(np.float32)
+    kept, tab = otab.build_table(scores, 59, 14, 14, 3)
+    n = tab.shape[0]
+    x = rng.standard_normal((n, 16)).astype(np.float32)
+    wt = rng.standard_normal((9, 16, 8)).astype(np.float32)
+    gy = rng.standard_normal((n, 8)).astype(np.float32)
+    sel = np.arange(3, n, 7)
+    np.testing.assert_array_equal(oconv.fwd(x, tab[sel], wt), oconv.fwd(x, tab, wt)[sel])
+    np.testing.assert_array_equal(oconv.dgrad_rows(gy, tab, wt, sel), oconv.dgrad(gy, tab, wt)[sel])
+    cs = [1, 5, 9]
+    np.testing.assert_array_equal(oconv.wgrad(gy, np.ascontiguousarray(x[:, cs]), tab, 9)[0],
+                                  oconv.wgrad(gy, x, tab, 9)[0][:, cs])
+    # batch-local tables: the sampled input gradient follows the same per-row offsets
+    tab_l = otab.initial_table(4, 4, 1, 1).reshape(-1, 9)
+    rep = np.tile(tab_l, (3, 1))
+    g2 = rng.standard_normal((48, 8)).astype(np.float32)
+    np.testing.assert_array_equal(oconv.dgrad_rows(g2, rep, wt, [0, 17, 47], 16), oconv.dgrad(g2, rep, wt, 16)[[0, 17, 47]])

@@ -2,8 +2,7 @@
 
 ``svtad_conv_wgrad_static`` is ``svtad_conv_wgrad`` with the workspace taken from an array built
 into the library, for hosts that must not call cudaMalloc once they are running (device memory owned
-by the host's own arena, allocation forbidden after start-up).  The test calls it through the C ABI twice in a row on different
-inputs - the array is shared and keeps the previous call's contents - and checks every result
+by the host's own arena, allocation forbidden after start-up).  The test calls it through the C ABI several times in a row - the array is shared and keeps the previous call's contents - and checks every result
 against the regular entry point and against the CPU oracle.
 """
 import numpy as np
@@ -32,10 +31,19 @@ def test_static_workspace_wgrad_matches_regular_entry_point_twice():
         gb = torch.full((C,), float("nan"), dtype=dtype, device="cuda")
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
-        for _ in range(2):                       # two calls in a row share the built-in array
+        free_before = None
+        for call in range(3):                    # calls in a row share the built-in array
             gw.fill_(float("nan")); gb.fill_(float("nan"))
+            torch.cuda.synchronize()
+            if call >= 1:
+                # From the second call on (the first may make the driver load the kernels' code), the device's free
+                # memory as the driver reports it must not move: that also sees a cudaMalloc made inside the
+                # library, which torch's own counters cannot.
+                free_before = torch.cuda.mem_get_info()[0]
             ops.conv_wgrad_static(gc, xc, tc, gw, gb)
             torch.cuda.synchronize()
+            if free_before is not None:
+                assert torch.cuda.mem_get_info()[0] == free_before, "device memory was allocated during the call"
             assert torch.cuda.memory_allocated() == before          # torch allocated nothing either
             assert torch.equal(gw, ref_gw) and torch.equal(gb, ref_gb)
         tol = 1e-5 if dtype == torch.float32 else 2e-2
