@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(FW_THREADS, 1)
 conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __restrict__ a,
                    const int32_t* __restrict__ nbr, const uint16_t* __restrict__ bias,
                    uint16_t* __restrict__ out, const int32_t* __restrict__ status, long n, int cred, int cn,
-                   int kk, int tpb, int nstage, int fp16, int m_tiles, int n_blks, int* __restrict__ err) {
+                   int kk, int tpb, int nstage, int fp16, int m_tiles, int n_blks, int out_al32, int* __restrict__ err) {
     if (DGRAD && status != nullptr && (__ldg(status) & SVTAD_TABLE_ASYMMETRIC)) return;
     constexpr int B_TILE_BYTES = b_tile_bytes_for(BN);
     constexpr int B_TX_BYTES = DGRAD ? BN * 128 : B_TILE_BYTES;
@@ -286,17 +286,21 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                 tmem_ld_wait();
                 if (c + 1 < NC) tmem_ld32(t_addr + (c + 1) * 32, (c & 1) ? va : vb);
                 if (row < n) {
-                    uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
                     const float4* b4 = reinterpret_cast<const float4*>(sb + c * 32);
+                    uint32_t o[16];
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        const float4 ba = b4[2 * g], bb = b4[2 * g + 1];
-                        uint4 o;
-                        o.x = pack2(__uint_as_float(v[g * 8 + 0]) + ba.x, __uint_as_float(v[g * 8 + 1]) + ba.y, fp16 != 0);
-                        o.y = pack2(__uint_as_float(v[g * 8 + 2]) + ba.z, __uint_as_float(v[g * 8 + 3]) + ba.w, fp16 != 0);
-                        o.z = pack2(__uint_as_float(v[g * 8 + 4]) + bb.x, __uint_as_float(v[g * 8 + 5]) + bb.y, fp16 != 0);
-                        o.w = pack2(__uint_as_float(v[g * 8 + 6]) + bb.z, __uint_as_float(v[g * 8 + 7]) + bb.w, fp16 != 0);
-                        dst[g] = o;
+                    for (int g = 0; g < 8; ++g) {
+                        const float4 ba = b4[g];
+                        o[2 * g] = pack2(__uint_as_float(v[g * 4 + 0]) + ba.x, __uint_as_float(v[g * 4 + 1]) + ba.y, fp16 != 0);
+                        o[2 * g + 1] = pack2(__uint_as_float(v[g * 4 + 2]) + ba.z, __uint_as_float(v[g * 4 + 3]) + ba.w, fp16 != 0);
+                    }
+                    if (out_al32) {      // one whole 32-byte sector per lane and store
+                        st_global_v8(orow + c * 32, &o[0]);
+                        st_global_v8(orow + c * 32 + 16, &o[8]);
+                    } else {
+                        uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) dst[g] = make_uint4(o[4 * g], o[4 * g + 1], o[4 * g + 2], o[4 * g + 3]);
                     }
                 }
             }
@@ -546,9 +550,10 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
 #pragma unroll
                     for (int g = 0; g < 8; ++g) dst[g] = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
                 } else if (dstrow != nullptr) {
-                    uint4* dst = reinterpret_cast<uint4*>(dstrow + c * 32);
+                    // 32 bytes (one whole sector) per store: the workspace is 256-byte aligned, rows are cout * 4 bytes
+                    float* dst = dstrow + c * 32;
 #pragma unroll
-                    for (int g = 0; g < 8; ++g) dst[g] = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                    for (int g = 0; g < 4; ++g) st_global_v8(dst + g * 8, &v[g * 8]);
                 }
             }
         }
@@ -638,7 +643,7 @@ static int launch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaStre
     int grid = (int)(tiles < tc_num_sms() ? tiles : tc_num_sms());
     SV_CUDA(tc_launch(kern, dim3(grid), dim3(FW_THREADS), smem, s, map_w, (const uint16_t*)p.a, p.nbr,
                       (const uint16_t*)p.bias, (uint16_t*)p.out, status, (long)p.n, cred, cn, p.kk, p.tpb, nstage, fp16,
-                      m_tiles, n_blks, tc_error_ptr()));
+                      m_tiles, n_blks, (reinterpret_cast<uintptr_t>(p.out) % 32 == 0) ? 1 : 0, tc_error_ptr()));
     return SVTAD_OK;
 }
 

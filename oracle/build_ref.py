@@ -5,7 +5,7 @@ Compiles the reference project's three extension sources
 the same list as the reference's setup.py:10-14) for sm_100a, straight from the
 reference checkout, into ``oracle/_ref/``, and byte-compiles the reference's Python wrapper
 (opentad/models/bricks/sparse_conv_layer.py) next to it.  Nothing is copied into this
-repository: only the built shared object and the compiled ``.pyc`` land in ``oracle/_ref/``
+repository: only the built shared object and the compiled bytecode file land in ``oracle/_ref/``
 (git-ignored).
 
 The result is used only by tests and by the benchmark's reference legs, as the
@@ -20,7 +20,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 NAME = "opentad_sparse_ops_ref"
-WRAPPER_PYC = os.path.join(OUT, "ref_sparse_conv_layer.pyc")
+WRAPPER_PYC = os.path.join(OUT, "ref_sparse_conv_layer.bytecode")
 
 
 def built_path():

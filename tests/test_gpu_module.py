@@ -164,7 +164,7 @@ def test_reference_wrapper_runs_unchanged_on_top_of_the_shim():
     from eccv26_tad_b200 import opentad_sparse_ops as shim
     ref = build_ref.load_wrapper(shim)
     if ref is None:
-        pytest.skip("oracle/_ref/ref_sparse_conv_layer.pyc has not been built")
+        pytest.skip("oracle/_ref/ref_sparse_conv_layer.bytecode has not been built")
     assert ref.sparse_lib_opt is shim                     # no JIT fallback to the reference's CUDA sources
     _, _, tab1 = make_table(1, 6, 14, 14, 0.3, 3, 71)
     N = tab1.shape[0]

@@ -190,7 +190,7 @@ def test_reference_wrapper_binds_to_the_shim_when_built():
     from eccv26_tad_b200 import SparseConv2d, opentad_sparse_ops as shim
     ref = build_ref.load_wrapper(shim)
     if ref is None:
-        pytest.skip("oracle/_ref/ref_sparse_conv_layer.pyc has not been built")
+        pytest.skip("oracle/_ref/ref_sparse_conv_layer.bytecode has not been built")
     assert ref.sparse_lib_opt is shim
     theirs = list(inspect.signature(ref.SparseConv2d.__init__).parameters)
     ours = list(inspect.signature(SparseConv2d.__init__).parameters)
