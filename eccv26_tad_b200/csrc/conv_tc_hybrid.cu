@@ -31,6 +31,13 @@
 
 namespace svtad {
 
+#ifdef SV_PROFILE
+__device__ long long g_prof[148 * 8];
+#define SV_T(x) const long long x = clock64()
+#else
+#define SV_T(x)
+#endif
+
 constexpr int HY_THREADS = 288;    // warps 0-3 producers, warp 4 MMA + TMEM owner, warps 5-8 epilogue
 constexpr int A_WARPS = 4;
 constexpr int A_THREADS = A_WARPS * 32;
@@ -39,6 +46,13 @@ constexpr int A_THREADS = A_WARPS * 32;
 #define SV_FW_A_WARPS 4
 #endif
 constexpr int FW_A_WARPS = SV_FW_A_WARPS;
+// warps that share the fill of one buffer
+#ifndef SV_FW_NPW
+#define SV_FW_NPW 1
+#endif
+constexpr int FW_NPW = SV_FW_NPW;
+constexpr int FW_GROUPS = FW_A_WARPS / FW_NPW;
+constexpr int FW_ITR = 32 / FW_NPW;          // 4-row copy iterations per lane and buffer
 constexpr int FW_A_THREADS = FW_A_WARPS * 32;
 constexpr int FW_THREADS = (FW_A_WARPS + 5) * 32;
 
@@ -88,10 +102,6 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
     const int sp_pad = RB == 2 ? ((stages_per_tile + 1) & ~1) : stages_per_tile;
     const int nbig = nstage / RB;             // nstage (number of 64-deep buffers) is a multiple of RB
     constexpr int RSH = RB == 2 ? 1 : 0;      // buffer -> barrier round
-    // Producer warps that take turns on the buffers.  Never more than there are buffers: a warp only waits for
-    // the consumer on its own steps, so with more warps than buffers one of them could run two rounds ahead of
-    // the consumer, where the parity of the empty barrier looks the same as "free", and refill a buffer in use.
-    const int n_prod = nstage < FW_A_WARPS ? nstage : FW_A_WARPS;
     const int tab_ints = TILE_M * kk;
 
     // raw table rows of a tile -> s_tab, by the producer threads, one tile ahead.  Behind them goes an L2 prefetch
@@ -119,7 +129,7 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
     }
     if (tid == 0) {
         for (int b = 0; b < nbig; ++b) {
-            mbar_init(smem_u32(&tail->full[b]), 33 * RB);    // per buffer: 32 copy arrivals + the TMA byte-count arrival
+            mbar_init(smem_u32(&tail->full[b]), (FW_NPW * 32 + 1) * RB);    // per buffer: the copies of the lanes that fill it + the TMA byte-count arrival
             mbar_init(smem_u32(&tail->empty[b]), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -139,6 +149,12 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
         // ------------------------------------------------------------------ producers
         const int sub = lane & 7, rg = lane >> 3;
         bool alive = true;
+        // FW_NPW warps share the fill of one buffer (each a FW_ITR * 4-row slice of it); the FW_A_WARPS / FW_NPW
+        // groups take turns on the K steps.  Never more groups than buffers: a group waits for the consumer only on
+        // its own steps, so with more groups than buffers one of them could run two rounds ahead of the consumer,
+        // where the parity of the empty barrier looks the same as "free", and refill a buffer in use.
+        const int grp = warp / FW_NPW, part = warp % FW_NPW;
+        const int n_own = nstage < FW_GROUPS ? nstage : FW_GROUPS;
         int local = 0;
         for (int tile = blockIdx.x; tile < tiles_total; tile += gridDim.x, ++local) {
             const long row0 = (long)(tile / n_blks) * TILE_M;
@@ -159,25 +175,26 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
             }
             named_bar_sync(1, FW_A_THREADS);
             if (tile + (int)gridDim.x < tiles_total) load_table(tile + gridDim.x);
-            if (!alive || warp >= n_prod) continue;   // keep taking part in the barriers above
+            if (!alive || grp >= n_own) continue;   // keep taking part in the barriers above
             const int it0 = local * sp_pad;
-            // first step of this tile that this warp owns; then every n_prod-th one.  Buffer, phase and
+            // first step of this tile that this warp's group owns; then every n_own-th one.  Buffer, phase and
             // (tap, chunk) advance incrementally: no division in the loop.
-            int st = ((warp - it0) % n_prod + n_prod) % n_prod;
-            int s = (it0 + st) % nstage;                         // 64-deep buffer; its barrier round is s >> 1
+            int st = ((grp - it0) % n_own + n_own) % n_own;
+            int s = (it0 + st) % nstage;                         // 64-deep buffer; its barrier round is s >> RSH
             uint32_t ph = (((it0 + st) / nstage) & 1) ^ 1;
             int k = st / kchunks, kc = st - k * kchunks;
-            for (; st < sp_pad; st += n_prod) {
+            for (; st < sp_pad; st += n_own) {
                 if (!warp_wait(smem_u32(&tail->empty[s >> RSH]), ph, s_abort, err, 41, lane)) { alive = false; break; }
                 const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
                 const uint32_t bar = smem_u32(&tail->full[s >> RSH]);
+                const bool tma_turn = lane == 0 && part == 0;
                 if (RB == 2 && st >= stages_per_tile) {
                     // the empty half of the tile's last round: same number of arrivals, nothing to copy
                     mbar_arrive(bar);
-                    if (lane == 0) mbar_arrive(bar);
+                    if (tma_turn) mbar_arrive(bar);
                 } else {
                     const int c0 = kc * STAGE_K;
-                    if (lane == 0) {
+                    if (tma_turn) {
                         const uint32_t b_tile = a_tile + A_TILE_BYTES;
                         const int wtap = DGRAD ? (kk - 1 - k) : k;
                         mbar_expect_tx(bar, B_TX_BYTES);
@@ -189,73 +206,91 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                             tma_load_3d(b_tile, &map_w, c0, n0, wtap, bar);
                         }
                     }
-                    // A: 128 rows x 8 chunks of 16 B; 8 consecutive lanes cover one row's 128 B
-                    const uint16_t* abase = a + c0 + sub * 8;
-                    // all row numbers first (eight 16-byte loads, the same for the 8 lanes of a row group), then
-                    // the copies back to back
-                    const int4* trow = reinterpret_cast<const int4*>(xf + (k << 7) + (rg << 5));
-                    int jrow[32];
+                    // this warp's rows are (FW_ITR * part + itr) * 4 + rg: all row numbers first (16-byte loads, the
+                    // same for the 8 lanes of a row group), then the copies back to back
+                    const int4* trow = reinterpret_cast<const int4*>(xf + (k << 7) + (rg << 5) + FW_ITR * part);
+                    int jrow[FW_ITR];
 #pragma unroll
-                    for (int q4 = 0; q4 < 8; ++q4) {
+                    for (int q4 = 0; q4 < FW_ITR / 4; ++q4) {
                         const int4 v = trow[q4];
                         jrow[4 * q4] = v.x; jrow[4 * q4 + 1] = v.y; jrow[4 * q4 + 2] = v.z; jrow[4 * q4 + 3] = v.w;
                     }
+                    // A: 8 consecutive lanes cover one row's 128 B (8 chunks of 16 B)
+                    const uint16_t* abase = a + c0 + sub * 8;
 #pragma unroll
-                    for (int itr = 0; itr < 32; ++itr) {
+                    for (int itr = 0; itr < FW_ITR; ++itr) {
                         const int j = jrow[itr];
-                        const int r7 = ((itr & 1) << 2) | rg;            // (row & 7) for row = itr * 4 + rg
-                        const uint32_t dst = a_tile + (itr * 4 + rg) * 128 + ((sub ^ r7) << 4);
+                        const int r7 = ((itr & 1) << 2) | rg;            // (row & 7) for row = (FW_ITR * part + itr) * 4 + rg
+                        const uint32_t dst = a_tile + ((FW_ITR * part + itr) * 4 + rg) * 128 + ((sub ^ r7) << 4);
                         cp_async16(dst, abase + (long)(j < 0 ? 0 : j) * cred, j < 0 ? 0u : 16u);
                     }
                     cp_async_arrive_noinc(bar);
                 }
-                s += n_prod;
+                s += n_own;
                 while (s >= nstage) { s -= nstage; ph ^= 1u; }
-                kc += n_prod;
+                kc += n_own;
                 while (kc >= kchunks) { kc -= kchunks; if (++k == kk) k = 0; }
             }
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
     } else if (warp == FW_A_WARPS) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // The whole warp walks the loop and waits; one elected lane (the same one every time) issues the MMAs and
+        // the commits.  Measured on B200 in a loop without data movement: 422 cycles per 64-deep step at BN = 192
+        // against 487 when a single diverged lane runs the loop by itself (the tensor pipe needs 384).
+        {
             const uint32_t idesc = make_idesc(fp16 ? 0 : 1, 0, DGRAD ? 0 : 1, TILE_M, BN);
             constexpr uint32_t desc_hi = smem_desc_hi(1024);
             bool alive = true;
             int local = 0, s = 0;
             uint32_t ph = 0;
-            bool ready = false;   // result of probing this step's barrier while the previous step's MMAs were issued
+#ifdef SV_PROFILE
+            long long p_wait = 0, p_first = 0;
+            const long long p_t0 = clock64();
+#endif
             for (int tile = blockIdx.x; tile < tiles_total && alive; tile += gridDim.x, ++local) {
                 const int buf = local & 1;
                 if (!mbar_wait(smem_u32(&tail->accum_empty[buf]), ((local >> 1) & 1) ^ 1, s_abort, err, 42)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int st = 0; st < sp_pad; st += RB) {
-                    if (!ready && !mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 43)) { alive = false; break; }
+                    SV_T(p_a);
+                    if (!mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 43)) { alive = false; break; }
+#ifdef SV_PROFILE
+                    { const long long d = clock64() - p_a; if (st == 0 && local == 0) p_first = d; else p_wait += d; }
+#endif
                     fence_proxy_async();   // cp.async (generic proxy) writes -> tcgen05.mma (async proxy) reads
+                    tc_fence_after();
                     const uint32_t a_tile = stage_base + (uint32_t)(RB * s) * STAGE_BYTES;
-                    int sn = s + 1;
-                    uint32_t phn = ph;
-                    if (sn == nbig) { sn = 0; phn ^= 1u; }
-                    ready = mbar_test_wait(smem_u32(&tail->full[sn]), phn);   // answer arrives while the MMAs issue
                     const int halves = (RB == 2 && st + 1 < stages_per_tile) ? 2 : 1;
-                    // descriptor low words: start address >> 4 (shared memory is below 256 KB, so adding a K step's
-                    // offset never carries into the LBO field above it)
-                    uint32_t a_lo = (a_tile & 0x3FFFFu) >> 4;
-                    for (int h = 0; h < halves; ++h) {
-                        const uint32_t b_lo = (a_lo + (A_TILE_BYTES >> 4)) | (DGRAD ? 0u : smem_desc_lbo_bits(8192));
-                        umma_f16_lh(d_tmem, a_lo, desc_hi, b_lo, desc_hi, idesc, (st | h) != 0 ? 1u : 0u);
+                    if (elect_one_sync()) {
+                        // descriptor low words: start address >> 4 (shared memory is below 256 KB, so adding a K step's
+                        // offset never carries into the LBO field above it)
+                        uint32_t a_lo = (a_tile & 0x3FFFFu) >> 4;
+                        for (int h = 0; h < halves; ++h) {
+                            const uint32_t b_lo = (a_lo + (A_TILE_BYTES >> 4)) | (DGRAD ? 0u : smem_desc_lbo_bits(8192));
+                            umma_f16_lh(d_tmem, a_lo, desc_hi, b_lo, desc_hi, idesc, (st | h) != 0 ? 1u : 0u);
 #pragma unroll
-                        for (int ks = 1; ks < STAGE_K / 16; ++ks)
-                            umma_f16_lh_acc(d_tmem, a_lo + ks * 2, desc_hi, b_lo + ks * (DGRAD ? 2 : 128), desc_hi, idesc);
-                        a_lo += STAGE_BYTES >> 4;
+                            for (int ks = 1; ks < STAGE_K / 16; ++ks)
+                                umma_f16_lh_acc(d_tmem, a_lo + ks * 2, desc_hi, b_lo + ks * (DGRAD ? 2 : 128), desc_hi, idesc);
+                            a_lo += STAGE_BYTES >> 4;
+                        }
+                        umma_commit(smem_u32(&tail->empty[s]));
                     }
-                    umma_commit(smem_u32(&tail->empty[s]));
-                    s = sn;
-                    ph = phn;
+                    __syncwarp();
+                    if (++s == nbig) { s = 0; ph ^= 1u; }
                 }
-                if (alive) umma_commit(smem_u32(&tail->accum_full[buf]));
+                if (!alive) break;
+                if (elect_one_sync()) umma_commit(smem_u32(&tail->accum_full[buf]));
+                __syncwarp();
             }
+#ifdef SV_PROFILE
+            if (lane == 0) {
+                g_prof[blockIdx.x * 8 + 0] = clock64() - p_t0;     // whole MMA loop
+                g_prof[blockIdx.x * 8 + 1] = p_wait;               // waiting for operands (all steps but the first)
+                g_prof[blockIdx.x * 8 + 2] = p_first;              // waiting for the first operands
+            }
+#endif
         }
     } else {
         // ------------------------------------------------------------------ epilogue (warps 5..8)
@@ -285,24 +320,7 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                 uint32_t (&v)[32] = (c & 1) ? vb : va;
                 tmem_ld_wait();
                 if (c + 1 < NC) tmem_ld32(t_addr + (c + 1) * 32, (c & 1) ? va : vb);
-                if (row < n) {
-                    const float4* b4 = reinterpret_cast<const float4*>(sb + c * 32);
-                    uint32_t o[16];
-#pragma unroll
-                    for (int g = 0; g < 8; ++g) {
-                        const float4 ba = b4[g];
-                        o[2 * g] = pack2(__uint_as_float(v[g * 4 + 0]) + ba.x, __uint_as_float(v[g * 4 + 1]) + ba.y, fp16 != 0);
-                        o[2 * g + 1] = pack2(__uint_as_float(v[g * 4 + 2]) + ba.z, __uint_as_float(v[g * 4 + 3]) + ba.w, fp16 != 0);
-                    }
-                    if (out_al32) {      // one whole 32-byte sector per lane and store
-                        st_global_v8(orow + c * 32, &o[0]);
-                        st_global_v8(orow + c * 32 + 16, &o[8]);
-                    } else {
-                        uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) dst[g] = make_uint4(o[4 * g], o[4 * g + 1], o[4 * g + 2], o[4 * g + 3]);
-                    }
-                }
+                if (row < n) store_row_chunk32(orow + c * 32, v, sb + c * 32, fp16 != 0, out_al32 != 0);
             }
             tc_fence_before();
             mbar_arrive(smem_u32(&tail->accum_empty[buf]));
@@ -336,7 +354,7 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     TmaTail* tail = reinterpret_cast<TmaTail*>(smem + (size_t)nstage * STAGE_BYTES);
-    int* s_idx = reinterpret_cast<int*>(tail + 1);                 // per producer warp: [2][STAGE_K * kk] table rows + [TILE_M] gather rows
+    int* s_idx = reinterpret_cast<int*>(tail + 1);                 // per producer warp: a ring of [2][128] table entries
     volatile int* s_abort = &tail->abort_flag;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -352,37 +370,52 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
     // second block of the last pair when the block count is odd: all ones, so its rows of D are sum_i gy[i,:]
     const bool ones_here = ones_block && !second_real;
 
-    // table rows of a warp's 64-token step, double buffered: [2][STAGE_K * kk] ints per warp
-    const int tab_ints = STAGE_K * kk;
-    int* my_tab = s_idx + warp * (2 * tab_ints + TILE_M);
-    int* my_rows = my_tab + 2 * tab_ints;              // [TILE_M] final gather rows of the current step
-    // CTAs of different block pairs walk the token range from different starting points (see the
-    // forward kernel); `src_stage` is the 64-token step that pipeline step `it` carries
+    // A producer warp owns every n_prod-th 64-token step.  The A tile of a step has 128 slots (slot = block * 64 +
+    // token); each lane looks up the table entry nbr[token, tap(block)] of the four slots lane + 32 * j.  The
+    // entries travel WG_PF own steps ahead of their use through a small ring in shared memory (4-byte cp.async,
+    // one commit group per own step).
+    constexpr int WG_PF = 2;
+    int* my_ent = s_idx + warp * (WG_PF * 128);         // [WG_PF][128] raw entries of this warp's coming steps
+    // CTAs of different block pairs walk the token range from different starting points; `src_stage` is the
+    // 64-token step that pipeline step `it` carries
     const int rot = total_stages > 0 ? (int)(((long)blockIdx.x * 5) % total_stages) : 0;
     auto src_stage = [&](int it) { int v = it + rot; return v >= total_stages ? v - total_stages : v; };
-    // the step's table rows are contiguous in memory: copy them whole (16-byte cp.async, rows past the
-    // end of this split read as zero bytes) one warp-iteration ahead; only these copies are committed
-    auto load_rows = [&](int sit, int buf) {
-        const long i0 = i_begin + (long)sit * STAGE_K;
-        const long rows = (i_end - i0) < STAGE_K ? (i_end - i0) : STAGE_K;
-        const int valid_bytes = (int)rows * kk * 4;
-        const char* src = reinterpret_cast<const char*>(nbr + i0 * kk);
-        const uint32_t dst = smem_u32(my_tab + buf * tab_ints);
-        for (int c = lane; c * 16 < tab_ints * 4; c += 32) {
-            int left = valid_bytes - c * 16;
-            uint32_t nb = left >= 16 ? 16u : (left > 0 ? (uint32_t)left : 0u);
-            cp_async16(dst + c * 16, nb ? src + c * 16 : src, nb);
-        }
-        cp_async_commit();
-    };
     // never more producer warps than buffers (see the forward kernel)
     const int n_prod = nstage < A_WARPS ? nstage : A_WARPS;
-    // the first step's rows start their trip before anything else is set up
-    if (warp < A_WARPS && warp < total_stages && warp < n_prod) {
-        load_rows(src_stage(warp), 0);
-        // and an L2 prefetch of the rows that step will gather (within a few dozen rows of its own tokens)
-        const long i0 = i_begin + (long)src_stage(warp) * STAGE_K;
-        if (lane == 31) l2_prefetch_rows(x, i0 - 64, i0 + STAGE_K + 64, n, cin);
+    int tap[2], ch0[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int blk = pair * 2 + h;
+        const bool real = blk < nblocks;
+        tap[h] = real ? blk / cblocks : 0;
+        ch0[h] = real ? (blk % cblocks) * 64 : 0;
+    }
+    // entries of own step number `own` (pipeline step warp + own * n_prod) -> ring slot own % WG_PF
+    auto load_entries = [&](int own) {
+        const int it = warp + own * n_prod;
+        if (it < total_stages) {
+            const long i0 = i_begin + (long)src_stage(it) * STAGE_K;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int slot = lane + 32 * j;
+                const int h = j >> 1, t = slot & 63;
+                const long i = i0 + t;
+                const bool ok = (h == 0 || second_real) && i < i_end;
+                const int32_t* src = nbr + (ok ? i * kk + tap[h] : 0);
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;"
+                             ::"r"(smem_u32(my_ent + (own % WG_PF) * 128 + slot)), "l"(src), "r"(ok ? 4u : 0u) : "memory");
+            }
+        }
+        cp_async_commit();     // one group per own step, empty or not: the wait below counts groups
+    };
+    // the first steps' entries start their trip before anything else is set up
+    if (warp < n_prod) {
+#pragma unroll
+        for (int own = 0; own < WG_PF; ++own) load_entries(own);
+        if (lane == 31 && warp < total_stages) {
+            const long i0 = i_begin + (long)src_stage(warp) * STAGE_K;
+            l2_prefetch_rows(x, i0 - 64, i0 + STAGE_K + 64, n, cin);
+        }
     }
     if (warp == 4) {
         tmem_alloc(smem_u32(&tail->tmem_slot), TM_COLS);
@@ -390,7 +423,7 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
     }
     if (tid == 0) {
         for (int s = 0; s < nstage; ++s) {
-            mbar_init(smem_u32(&tail->full[s]), 33);
+            mbar_init(smem_u32(&tail->full[s]), 33);     // the owning warp's 32 copy arrivals + the TMA byte count
             mbar_init(smem_u32(&tail->empty[s]), 1);
         }
         mbar_init(smem_u32(&tail->accum_full[0]), 1);
@@ -416,49 +449,33 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
             fence_proxy_async();
             named_bar_sync(1, A_THREADS);
         }
-        int tap[2], ch0[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            int blk = pair * 2 + h;
-            bool real = blk < nblocks;
-            tap[h] = real ? blk / cblocks : 0;
-            ch0[h] = real ? (blk % cblocks) * 64 : 0;
-        }
         const int sub = lane & 7, rg = lane >> 3;
-        int local = 0;
         int s = warp % nstage;
         uint32_t ph = ((warp / nstage) & 1) ^ 1;
-        const int rows = second_real ? 32 : 16;            // slots 64..127 belong to the second block
-        for (int it = warp; it < total_stages && warp < n_prod; it += n_prod, ++local) {
-            const int* tab = my_tab + (local & 1) * tab_ints;
-            cp_async_wait<0>();
-            __syncwarp();
-            if (it + n_prod < total_stages) load_rows(src_stage(it + n_prod), (local & 1) ^ 1);
-            // each lane turns four slots (slot = block * 64 + token) into final gather rows, the warp shares them
-            // through shared memory, and every lane then holds the rows of the 32 slots it copies
+        const int rows_n = second_real ? 32 : 16;            // slots 64..127 belong to the second block
+        int own = 0;
+        for (int it = warp; it < total_stages && warp < n_prod; it += n_prod, ++own) {
+            // this own step's entries have landed (the WG_PF - 1 younger groups may still be in flight)
+            cp_async_wait<WG_PF - 1>();
             const long i0 = i_begin + (long)src_stage(it) * STAGE_K;
-            {
-                int v4[4];
+            int v[4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int slot = lane * 4 + j;
-                    const int h = slot >> 6, t = slot & 63;
-                    const long i = i0 + t;
-                    int v = -1;
-                    if ((h == 0 || second_real) && i < i_end) {
-                        const int raw = tab[t * kk + tap[h]];
-                        const long jj = (long)raw + (tpb > 0 ? (i / tpb) * (long)tpb : 0);
-                        if (raw >= 0 && jj < n) v = (int)jj;
-                    }
-                    v4[j] = v;
+            for (int j = 0; j < 4; ++j) {
+                const int slot = lane + 32 * j;
+                const int h = j >> 1, t = slot & 63;
+                const long i = i0 + t;
+                v[j] = -1;
+                if ((h == 0 || second_real) && i < i_end) {
+                    const int raw = my_ent[(own % WG_PF) * 128 + slot];
+                    const long jj = (long)raw + (tpb > 0 ? (i / tpb) * (long)tpb : 0);
+                    if (raw >= 0 && jj < n) v[j] = (int)jj;
                 }
-                *reinterpret_cast<int4*>(my_rows + lane * 4) = make_int4(v4[0], v4[1], v4[2], v4[3]);
             }
-            __syncwarp();
+            load_entries(own + WG_PF);       // the ring slot just read is free again (each lane reads only what it copied)
+            // the rows this lane copies: slot itr * 4 + rg is held by lane (itr & 7) * 4 + rg in v[itr >> 3]
             int jrow[32];
 #pragma unroll
-            for (int itr = 0; itr < 32; ++itr) jrow[itr] = my_rows[itr * 4 + rg];
-            __syncwarp();
+            for (int itr = 0; itr < 32; ++itr) jrow[itr] = __shfl_sync(0xffffffffu, v[itr >> 3], (itr & 7) * 4 + rg);
             if (!warp_wait(smem_u32(&tail->empty[s]), ph, s_abort, err, 51, lane)) break;
             const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
             const uint32_t bar = smem_u32(&tail->full[s]);
@@ -471,7 +488,7 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
             }
 #pragma unroll
             for (int itr = 0; itr < 32; ++itr) {
-                if (itr < rows) {
+                if (itr < rows_n) {
                     const int r = itr * 4 + rg;
                     const int j = jrow[itr];
                     const int r7 = ((itr & 1) << 2) | rg;
@@ -486,20 +503,17 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
     } else if (warp == 4) {
-        if (lane == 0) {
-            const uint32_t idesc = make_idesc(fp16 ? 0 : 1, 1, 1, TILE_M, BN);
-            bool alive = true;
-            int s = 0;
-            uint32_t ph = 0;
-            bool ready = false;
-            for (int it = 0; it < total_stages; ++it) {
-                if (!ready && !mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 52)) { alive = false; break; }
-                fence_proxy_async();
-                const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
-                int sn = s + 1;
-                uint32_t phn = ph;
-                if (sn == nstage) { sn = 0; phn ^= 1u; }
-                ready = mbar_test_wait(smem_u32(&tail->full[sn]), phn);
+        // the whole warp walks the loop and waits; one elected lane issues the MMAs and the commits
+        const uint32_t idesc = make_idesc(fp16 ? 0 : 1, 1, 1, TILE_M, BN);
+        bool alive = true;
+        int s = 0;
+        uint32_t ph = 0;
+        for (int it = 0; it < total_stages; ++it) {
+            if (!mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 52)) { alive = false; break; }
+            fence_proxy_async();
+            tc_fence_after();
+            const uint32_t a_tile = stage_base + (uint32_t)s * STAGE_BYTES;
+            if (elect_one_sync()) {
                 // both operands MN-major: 16 K rows per step = 2048 B, 64-element blocks 8192 B apart
                 const uint32_t a_lo = ((a_tile & 0x3FFFFu) >> 4) | smem_desc_lbo_bits(8192);
                 const uint32_t b_lo = a_lo + (A_TILE_BYTES >> 4);
@@ -508,11 +522,12 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
                 for (int ks = 1; ks < STAGE_K / 16; ++ks)
                     umma_f16_lh_acc(tmem_base, a_lo + ks * 128, smem_desc_hi(1024), b_lo + ks * 128, smem_desc_hi(1024), idesc);
                 umma_commit(smem_u32(&tail->empty[s]));
-                s = sn;
-                ph = phn;
             }
-            if (alive && total_stages > 0) umma_commit(smem_u32(&tail->accum_full[0]));
+            __syncwarp();
+            if (++s == nstage) { s = 0; ph ^= 1u; }
         }
+        if (alive && total_stages > 0 && elect_one_sync()) umma_commit(smem_u32(&tail->accum_full[0]));
+        __syncwarp();
     } else {
         // epilogue: fp32 partial tile -> ws_w[split][(tap, ci)][co]; the all-ones block -> ws_b[split][co]
         bool have = true;
@@ -632,7 +647,7 @@ static int launch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaStre
     if (nstage < 2)
         return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core conv: not enough shared memory for BN=%d kk=%d", BN, p.kk);
     // rounds of two buffers once three rounds fit (narrow column blocks); otherwise one buffer per round
-    const bool two = nstage >= 6;
+    const bool two = nstage >= 6 || (getenv("SVTAD_X_RB2") != nullptr && nstage >= 4);
     if (two) nstage &= ~1;
     const size_t smem = 1024 + nstage * stage + extra;
     auto kern = two ? conv_hybrid_kernel<BN, DGRAD, 2> : conv_hybrid_kernel<BN, DGRAD, 1>;
@@ -661,6 +676,12 @@ static int dispatch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaSt
     return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core conv: no column block for width %d", cn);
 }
 
+#ifdef SV_PROFILE
+extern "C" int svtad_prof_read(long long* out) {
+    return cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 148 * 8) == cudaSuccess ? 0 : 1;
+}
+#endif
+
 int hybrid_fwd(const ConvArgs& p, cudaStream_t s) { return dispatch_conv_hybrid<false>(p, nullptr, s); }
 int hybrid_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s) { return dispatch_conv_hybrid<true>(p, status, s); }
 
@@ -676,7 +697,7 @@ static int launch_wgrad_hybrid(const void* gy, const void* x, const int32_t* nbr
         if (rc) return rc;
     }
     const size_t stage = A_TILE_BYTES + b_tile_bytes_for(BN);
-    const size_t extra = sizeof(TmaTail) + (size_t)A_WARPS * (2 * STAGE_K * kk + TILE_M) * sizeof(int);
+    const size_t extra = sizeof(TmaTail) + (size_t)A_WARPS * 2 * 128 * sizeof(int);
     int nstage = (int)((TC_SMEM_LIMIT - 1024 - extra) / stage);
     if (nstage > 8) nstage = 8;
     if (nstage < 2)

@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(PR_THREADS, 1)
 conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __restrict__ a,
                  const int32_t* __restrict__ nbr, const uint16_t* __restrict__ bias,
                  uint16_t* __restrict__ out, const int32_t* __restrict__ status, long n, int cred, int cn,
-                 int kk, int tpb, int nstage, int fp16, int m_pairs, int n_blks, int* __restrict__ err) {
+                 int kk, int tpb, int nstage, int fp16, int m_pairs, int n_blks, int out_al32, int* __restrict__ err) {
     // uniform over the whole grid, so both CTAs of a pair leave together
     if (DGRAD && status != nullptr && (__ldg(status) & SVTAD_TABLE_ASYMMETRIC)) return;
     constexpr int HALF = BN / 2;                  // columns of B this CTA stages
@@ -266,13 +266,13 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
     } else if (warp == 4) {
-        if (lane == 0 && rank == 0) {
+        if (rank == 0) {
             // ------------------------------------------------------------------ MMA issuer (even CTA)
+            // the whole warp walks the loop and waits; one elected lane (the same every time) issues and commits
             const uint32_t idesc = make_idesc(fp16 ? 0 : 1, 0, DGRAD ? 0 : 1, 2 * TILE_M, BN);
             bool alive = true;
             int local = 0, s = 0;
             uint32_t ph = 0;
-            bool ready = false;   // result of probing this step's barrier while the previous step's MMAs were issued
             // distance from one of this CTA's shared-memory addresses to the same location in the odd CTA
             const uint32_t to_peer = map_to_cta(stage_base, 1) - stage_base;
             for (int item = cid; item < items_total && alive; item += n_clusters, ++local) {
@@ -281,39 +281,40 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int st = 0; st < sp_pad; st += 2) {
-                    if (!ready && !mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 53)) { alive = false; break; }
+                    if (!mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 53)) { alive = false; break; }
                     fence_proxy_async();
+                    tc_fence_after();
                     const uint32_t a_tile = stage_base + (uint32_t)(2 * s) * STAGE_BYTES;
-                    int sn = s + 1;
-                    uint32_t phn = ph;
-                    if (sn == nbig) { sn = 0; phn ^= 1u; }
-                    ready = mbar_test_wait(smem_u32(&tail->full[sn]), phn);
                     const int halves = (st + 1 < stages_per_tile) ? 2 : 1;
-                    // descriptor low words (start address >> 4, LBO field); the high words are constants.
-                    // forward B: 16 K rows of 64 B per step (1024 B), 8-row groups 512 B apart, 32-column atoms
-                    // 4 KB apart, 64-byte swizzle (layout code 4)
-                    uint32_t a_lo = (a_tile & 0x3FFFFu) >> 4;
-                    constexpr uint32_t a_hi = smem_desc_hi(1024);
-                    constexpr uint32_t b_hi = DGRAD ? smem_desc_hi(1024) : (((512u >> 4) & 0x3FFFu) | (1u << 14) | (4u << 29));
-                    for (int h = 0; h < halves; ++h) {
-                        const uint32_t b_lo = (a_lo + (A_TILE_BYTES >> 4)) | (DGRAD ? 0u : smem_desc_lbo_bits(4096));
+                    if (elect_one_sync()) {
+                        // descriptor low words (start address >> 4, LBO field); the high words are constants.
+                        // forward B: 16 K rows of 64 B per step (1024 B), 8-row groups 512 B apart, 32-column atoms
+                        // 4 KB apart, 64-byte swizzle (layout code 4)
+                        uint32_t a_lo = (a_tile & 0x3FFFFu) >> 4;
+                        constexpr uint32_t a_hi = smem_desc_hi(1024);
+                        constexpr uint32_t b_hi = DGRAD ? smem_desc_hi(1024) : (((512u >> 4) & 0x3FFFu) | (1u << 14) | (4u << 29));
+                        for (int h = 0; h < halves; ++h) {
+                            const uint32_t b_lo = (a_lo + (A_TILE_BYTES >> 4)) | (DGRAD ? 0u : smem_desc_lbo_bits(4096));
 #pragma unroll
-                        for (int ks = 0; ks < STAGE_K / 16; ++ks)
-                            umma_pair_f16_lh(d_tmem, a_lo + ks * 2, a_hi, b_lo + ks * (DGRAD ? 2 : 64), b_hi, idesc,
-                                             ks != 0 ? 1u : ((st | h) != 0 ? 1u : 0u));
-                        a_lo += STAGE_BYTES >> 4;
+                            for (int ks = 0; ks < STAGE_K / 16; ++ks)
+                                umma_pair_f16_lh(d_tmem, a_lo + ks * 2, a_hi, b_lo + ks * (DGRAD ? 2 : 64), b_hi, idesc,
+                                                 ks != 0 ? 1u : ((st | h) != 0 ? 1u : 0u));
+                            a_lo += STAGE_BYTES >> 4;
+                        }
+                        const uint32_t e_local = smem_u32(&tail->empty[s]);
+                        umma_pair_commit(e_local);
+                        umma_pair_commit(e_local + to_peer);
                     }
-                    const uint32_t e_local = smem_u32(&tail->empty[s]);
-                    umma_pair_commit(e_local);
-                    umma_pair_commit(e_local + to_peer);
-                    s = sn;
-                    ph = phn;
+                    __syncwarp();
+                    if (++s == nbig) { s = 0; ph ^= 1u; }
                 }
-                if (alive) {
+                if (!alive) break;
+                if (elect_one_sync()) {
                     const uint32_t f_local = smem_u32(&tail->accum_full[buf]);
                     umma_pair_commit(f_local);
                     umma_pair_commit(f_local + to_peer);
                 }
+                __syncwarp();
             }
         } else if (lane == 0) {
             // ------------------------------------------------------------------ relay (odd CTA)
@@ -353,20 +354,7 @@ conv_pair_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __re
                 uint32_t (&v)[32] = (c & 1) ? vb : va;
                 tmem_ld_wait();
                 if (c + 1 < NC) tmem_ld32(t_addr + (c + 1) * 32, (c & 1) ? va : vb);
-                if (row < n) {
-                    uint4* dst = reinterpret_cast<uint4*>(orow + c * 32);
-                    const float4* b4 = reinterpret_cast<const float4*>(sb + c * 32);
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        const float4 ba = b4[2 * g], bb = b4[2 * g + 1];
-                        uint4 o;
-                        o.x = pack2(__uint_as_float(v[g * 8 + 0]) + ba.x, __uint_as_float(v[g * 8 + 1]) + ba.y, fp16 != 0);
-                        o.y = pack2(__uint_as_float(v[g * 8 + 2]) + ba.z, __uint_as_float(v[g * 8 + 3]) + ba.w, fp16 != 0);
-                        o.z = pack2(__uint_as_float(v[g * 8 + 4]) + bb.x, __uint_as_float(v[g * 8 + 5]) + bb.y, fp16 != 0);
-                        o.w = pack2(__uint_as_float(v[g * 8 + 6]) + bb.z, __uint_as_float(v[g * 8 + 7]) + bb.w, fp16 != 0);
-                        dst[g] = o;
-                    }
-                }
+                if (row < n) store_row_chunk32(orow + c * 32, v, sb + c * 32, fp16 != 0, out_al32 != 0);
             }
             tc_fence_before();
             __syncwarp();
@@ -435,7 +423,7 @@ static int launch_conv_pair(const ConvArgs& p, const int32_t* status, cudaStream
     cfg.numAttrs = 1;
     SV_CUDA(cudaLaunchKernelEx(&cfg, kern, map_w, (const uint16_t*)p.a, p.nbr, (const uint16_t*)p.bias,
                                (uint16_t*)p.out, status, (long)p.n, cred, cn, p.kk, p.tpb, nstage, fp16, m_pairs,
-                               n_blks, tc_error_ptr()));
+                               n_blks, (reinterpret_cast<uintptr_t>(p.out) % 32 == 0) ? 1 : 0, tc_error_ptr()));
     return SVTAD_OK;
 }
 

@@ -85,6 +85,12 @@ __device__ __forceinline__ void tmem_relinquish() {
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
+// one lane of the (converged) warp returns true - the same lane every time for a full mask
+__device__ __forceinline__ bool elect_one_sync() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -184,6 +190,28 @@ __device__ __forceinline__ float widen(uint16_t v, bool fp16) {
     return __uint_as_float(static_cast<uint32_t>(v) << 16);
 }
 
+// 32 accumulator columns of one output row: + bias (fp32), one rounding, 64 bytes to `dst` - as two whole 32-byte
+// sectors when the row is 32-byte aligned, else as four 16-byte stores
+__device__ __forceinline__ void store_row_chunk32(uint16_t* dst, const uint32_t (&v)[32], const float* bias32, bool fp16,
+                                                  bool al32) {
+    const float4* b4 = reinterpret_cast<const float4*>(bias32);
+    uint32_t o[16];
+#pragma unroll
+    for (int g = 0; g < 8; ++g) {
+        const float4 ba = b4[g];
+        o[2 * g] = pack2(__uint_as_float(v[g * 4 + 0]) + ba.x, __uint_as_float(v[g * 4 + 1]) + ba.y, fp16);
+        o[2 * g + 1] = pack2(__uint_as_float(v[g * 4 + 2]) + ba.z, __uint_as_float(v[g * 4 + 3]) + ba.w, fp16);
+    }
+    if (al32) {
+        st_global_v8(dst, &o[0]);
+        st_global_v8(dst + 16, &o[8]);
+    } else {
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) d4[g] = make_uint4(o[4 * g], o[4 * g + 1], o[4 * g + 2], o[4 * g + 3]);
+    }
+}
+
 // bytes of one B stage: MN-major tiles are whole 64-column blocks of 8 KB, K-major tiles BN rows of 128 B
 constexpr int b_tile_bytes_for(int bn) { return ((bn + 63) / 64) * 8192; }
 constexpr int tmem_cols_for(int bn) { return bn <= 32 ? 32 : bn <= 64 ? 64 : bn <= 128 ? 128 : 256; }
@@ -259,6 +287,10 @@ struct WgradPlan {
 };
 WgradPlan tc_wgrad_plan(int64_t n, int cin, int cout, int kk);
 size_t tc_wgrad_plan_ws_bytes(int64_t n, int cin, int cout, int kk);
+WgradPlan tc_wgrad_plan_with(int64_t n, int cin, int cout, int kk, int bn, long other_items, int other_steps);
+// one-launch backward (conv_tc_multi.cu)
+bool multi_bwd_supported(int64_t n, int cin, int cout, int kk);
+WgradPlan multi_bwd_plan(int64_t n, int cin, int cout, int kk);
 // fixed-order reduction of per-split fp32 partials into the 16-bit gradient tensors
 int tc_wgrad_reduce_launch(const float* ws_w, int splits, const float* ws_b, int splits_b, void* gw, void* gb,
                            long n_w, int cout, int fp16, cudaStream_t s);

@@ -29,6 +29,7 @@ def _no_forced_path(monkeypatch):
     monkeypatch.delenv("SVTAD_TC_BN", raising=False)
     monkeypatch.delenv("SVTAD_TC_WGRAD_CLUSTER", raising=False)
     monkeypatch.delenv("SVTAD_TC_IMPL", raising=False)
+    monkeypatch.delenv("SVTAD_TC_FUSED_BWD", raising=False)
     yield
     assert _ops().device_error() == 0, "a bounded wait inside a tensor-core kernel gave up"
 
@@ -415,6 +416,71 @@ def test_one_call_backward_equals_the_two_halves(dtype, C, kind, monkeypatch):
     ref = torch.stack([gx0.float().sum(), gw0.float().sum(), gb0.float().sum()])
     assert torch.equal(sums[1:], ref[1:])
     assert torch.equal(sums[:1], ref[:1]) if kind == "geometric" else abs(float(sums[0] - ref[0])) <= 1e-2 * float(gx0.float().abs().sum())
+
+
+def _fused_bwd(table, x, w, gy, tpb=0):
+    ops = _ops()
+    tc, xc, wc, gc = (t.cuda() for t in (table, x, w, gy))
+    gx, gw, gb = ops.conv_bwd(gc, xc, tc, wc, tpb, assume_symmetric=True)
+    torch.cuda.synchronize()
+    return gx, gw, gb
+
+
+@pytest.mark.parametrize("C,ks,dtype,shape", [
+    (192, 3, torch.bfloat16, (2, 80, 0.10)),     # the benchmark's three layers
+    (192, 3, torch.bfloat16, (2, 80, 0.30)),
+    (192, 3, torch.bfloat16, (2, 80, 0.55)),
+    (192, 3, torch.float16, (1, 3, 0.55)),
+    (64, 3, torch.bfloat16, (1, 9, 0.3)),
+    (128, 3, torch.bfloat16, (1, 7, 1.0)),
+    (256, 5, torch.bfloat16, (1, 6, 0.3)),
+    (768, 3, torch.bfloat16, (1, 6, 0.3)),       # three column blocks per row tile and per block pair
+    (192, 3, torch.bfloat16, (1, 1, 0.02)),      # 4 rows: one tile, one split
+])
+def test_one_launch_backward_against_oracle(C, ks, dtype, shape):
+    """The backward of a layer as ONE launch over a work list (input-gradient tiles + weight-gradient items), taken
+    when the caller vouches for a symmetric table: both gradients against the oracle, the input gradient bitwise
+    equal to the stand-alone kernel's, and bitwise repeatable."""
+    ops = _ops()
+    B, T, keep = shape
+    _, _, table = make_table(B, T, 14, 14, keep, ks, 55)
+    n = table.shape[0]
+    x, w, b, gy = make_conv_inputs(n, C, C, ks, dtype, 55, bias="random")
+    gx, gw, gb = _fused_bwd(table, x, w, gy)
+    tn = table.numpy()
+    xf, wf, gf = (f32np(t) for t in (x, w, gy))
+    assert oconv.rel_err(f32np(gx), oconv.dgrad(gf, tn, wf)) < 2e-2
+    egw, egb = oconv.wgrad(gf, xf, tn, ks * ks)
+    assert oconv.rel_err(f32np(gw), egw) < 2e-2 and oconv.rel_err(f32np(gb), egb) < 2e-2
+    gx0 = ops.conv_dgrad(gy.cuda(), table.cuda(), w.cuda(), assume_symmetric=True)
+    assert torch.equal(gx, gx0)
+    for _ in range(3):
+        again = _fused_bwd(table, x, w, gy)
+        for u, v in zip((gx, gw, gb), again):
+            assert torch.equal(u, v)
+
+
+def test_one_launch_backward_ragged_rows_and_batch_local_indices():
+    for n in (1, 129, 1000):
+        table = _chain_table(n)
+        x, w, b, gy = make_conv_inputs(n, 192, 192, 3, torch.bfloat16, n, bias="random")
+        gx, gw, gb = _fused_bwd(table, x, w, gy)
+        tn = table.numpy()
+        xf, wf, gf = (f32np(t) for t in (x, w, gy))
+        assert oconv.rel_err(f32np(gx), oconv.dgrad(gf, tn, wf)) < 2e-2
+        egw, egb = oconv.wgrad(gf, xf, tn, 9)
+        assert oconv.rel_err(f32np(gw), egw) < 2e-2 and oconv.rel_err(f32np(gb), egb) < 2e-2
+    _, _, glob = make_table(3, 4, 14, 14, 0.3, 3, 9)
+    n = glob.shape[0]
+    tpb = n // 3
+    local = glob.clone()
+    local[local >= 0] %= tpb
+    x, w, b, gy = make_conv_inputs(n, 128, 128, 3, torch.bfloat16, 9, bias="random")
+    gx, gw, gb = _fused_bwd(local, x, w, gy, tpb=tpb)
+    xf, wf, gf = (f32np(t) for t in (x, w, gy))
+    assert oconv.rel_err(f32np(gx), oconv.dgrad(gf, local.numpy(), wf, tpb)) < 2e-2
+    egw, egb = oconv.wgrad(gf, xf, local.numpy(), 9, tpb)
+    assert oconv.rel_err(f32np(gw), egw) < 2e-2 and oconv.rel_err(f32np(gb), egb) < 2e-2
 
 
 def test_determinism_of_backward():
