@@ -198,18 +198,6 @@ extern "C" int svtad_conv_bwd(const void* gy, const void* x, const int32_t* nbr,
                          w_part + d_part);
     void* ws_d = d_part ? static_cast<char*>(workspace) + w_part : nullptr;
     cudaStream_t s = (cudaStream_t)stream;
-    // Symmetric table vouched for by the caller, 16-bit tensors: both gradients in ONE launch over a work list of
-    // input-gradient tiles and weight-gradient items (conv_tc_multi.cu), then the reduction of the partials.
-    if (table_status == nullptr && n > 0 && use_tc(SVTAD_OP_BWD, n, cin, cout, kk, dtype) &&
-        tc_bwd_fused_supported(n, cin, cout, kk, dtype)) {
-        int rc = check_common("svtad_conv_bwd", n, cin, cout, kk, tokens_per_batch, dtype);
-        if (rc) return rc;
-        SV_CHECK_ARG(gy && x && nbr && w, "svtad_conv_bwd: null pointer");
-        SV_CHECK_ARG(aligned(gy, 16) && aligned(x, 16) && aligned(w, 16) && aligned(gx, 16) && aligned(gw, 16) &&
-                     aligned(nbr, 16) && aligned(gb, 16) && aligned(workspace, 256),
-                     "svtad_conv_bwd: gy, x, nbr, w, gx, gw and gb must be 16-byte aligned, the workspace 256-byte aligned");
-        return tc_bwd_fused(gy, x, nbr, w, gx, gw, gb, n, cin, cout, kk, tokens_per_batch, dtype, workspace, w_part, s);
-    }
     int dev = 0;
     SV_CUDA(cudaGetDevice(&dev));
     if (!overlap_backward() || n == 0 || dev >= MAX_DEVICES) {

@@ -78,10 +78,6 @@ int tc_read_error(int32_t* code_out);
                        int cin, int cout, int kk, int tpb, int dtype, void* ws, size_t ws_bytes,            \
                        cudaStream_t s);
 SV_DECLARE_TC_FAMILY(hybrid)
-// the backward of a layer as one launch over a work list (conv_tc_multi.cu)
-bool tc_bwd_fused_supported(int64_t n, int cin, int cout, int kk, int dtype);
-int tc_bwd_fused(const void* gy, const void* x, const int32_t* nbr, const void* w, void* gx, void* gw, void* gb,
-                 int64_t n, int cin, int cout, int kk, int tpb, int dtype, void* ws, size_t ws_bytes, cudaStream_t s);
 // forward / dgrad on CTA pairs (conv_tc_pair.cu)
 int pair_fwd(const ConvArgs& p, cudaStream_t s);
 int pair_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s);

@@ -199,49 +199,6 @@ WgradPlan tc_wgrad_plan(int64_t n, int cin, int cout, int kk) {
     return pl;
 }
 
-// Split of the weight gradient when its items share one work list (and the SMs) with `other_items` items of
-// `other_steps` K steps each (the input-gradient tiles of the same layer): CTA c of `sms` takes items c, c + sms,
-// ...; the split that makes the busiest CTA's step count smallest wins, ties to fewer splits.
-WgradPlan tc_wgrad_plan_with(int64_t n, int cin, int cout, int kk, int bn, long other_items, int other_steps) {
-    WgradPlan pl;
-    pl.bn = bn;
-    pl.n_nblk = cout / bn;
-    const int nblocks = kk * (cin / 64);
-    pl.n_pairs = (nblocks + 1) / 2;
-    pl.ones_block = nblocks & 1;
-    pl.cluster = 0;
-    const long ctas = (long)pl.n_pairs * pl.n_nblk;
-    const long sms = tc_num_sms();
-    long max_by_rows = (n + 2 * STAGE_K - 1) / (2 * STAGE_K);
-    if (max_by_rows < 1) max_by_rows = 1;
-    if (max_by_rows > 64) max_by_rows = 64;
-    const int per_item = 6;                       // fixed cost of an item, in K steps
-    long best_s = 1;
-    long best_cost = -1;
-    for (long c = 1; c <= max_by_rows; ++c) {
-        const long tps = ((n + c - 1) / c + STAGE_K - 1) / STAGE_K * STAGE_K;
-        const long splits = (n + tps - 1) / tps;
-        const long w_items = ctas * splits;
-        const long w_steps = tps / STAGE_K + per_item;
-        const long total = w_items + other_items;
-        // CTA c's load: items c, c + sms, ...; the first w_items items are weight-gradient items
-        long worst = 0;
-        const long probe = total < sms ? total : sms;
-        for (long cta = 0; cta < probe; ++cta) {
-            long load = 0;
-            for (long it = cta; it < total; it += sms) load += it < w_items ? w_steps : other_steps + per_item;
-            if (load > worst) worst = load;
-        }
-        if (best_cost < 0 || worst * 100 < best_cost * 98) { best_cost = worst; best_s = c; }
-    }
-    const char* e = getenv("SVTAD_TC_WGRAD_SPLITS");
-    if (e != nullptr && *e && atoi(e) > 0) best_s = atoi(e) < max_by_rows ? atoi(e) : max_by_rows;
-    const long tps = ((n + best_s - 1) / best_s + STAGE_K - 1) / STAGE_K * STAGE_K;
-    pl.tokens_per_split = tps;
-    pl.splits = (int)((n + tps - 1) / tps);
-    return pl;
-}
-
 static size_t plan_bytes(const WgradPlan& pl, int64_t n, int cin, int cout, int kk) {
     size_t w = (size_t)pl.splits * kk * cin * cout * sizeof(float);
     int sb = pl.ones_block ? pl.splits : bias_splits_for(n);
@@ -249,14 +206,8 @@ static size_t plan_bytes(const WgradPlan& pl, int64_t n, int cin, int cout, int 
     return align_up(w, 256) + align_up(b, 256);
 }
 
-// the larger of what the stand-alone weight gradient and the one-launch backward need
 size_t tc_wgrad_plan_ws_bytes(int64_t n, int cin, int cout, int kk) {
-    size_t a = plan_bytes(tc_wgrad_plan(n, cin, cout, kk), n, cin, cout, kk);
-    if (multi_bwd_supported(n, cin, cout, kk)) {
-        size_t b = plan_bytes(multi_bwd_plan(n, cin, cout, kk), n, cin, cout, kk);
-        if (b > a) a = b;
-    }
-    return a;
+    return plan_bytes(tc_wgrad_plan(n, cin, cout, kk), n, cin, cout, kk);
 }
 
 size_t tc_wgrad_ws_bytes(int64_t n, int cin, int cout, int kk) { return tc_wgrad_plan_ws_bytes(n, cin, cout, kk); }

@@ -31,13 +31,6 @@
 
 namespace svtad {
 
-#ifdef SV_PROFILE
-__device__ long long g_prof[148 * 8];
-#define SV_T(x) const long long x = clock64()
-#else
-#define SV_T(x)
-#endif
-
 constexpr int HY_THREADS = 288;    // warps 0-3 producers, warp 4 MMA + TMEM owner, warps 5-8 epilogue
 constexpr int A_WARPS = 4;
 constexpr int A_THREADS = A_WARPS * 32;
@@ -244,21 +237,13 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
             bool alive = true;
             int local = 0, s = 0;
             uint32_t ph = 0;
-#ifdef SV_PROFILE
-            long long p_wait = 0, p_first = 0;
-            const long long p_t0 = clock64();
-#endif
             for (int tile = blockIdx.x; tile < tiles_total && alive; tile += gridDim.x, ++local) {
                 const int buf = local & 1;
                 if (!mbar_wait(smem_u32(&tail->accum_empty[buf]), ((local >> 1) & 1) ^ 1, s_abort, err, 42)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int st = 0; st < sp_pad; st += RB) {
-                    SV_T(p_a);
                     if (!mbar_wait(smem_u32(&tail->full[s]), ph, s_abort, err, 43)) { alive = false; break; }
-#ifdef SV_PROFILE
-                    { const long long d = clock64() - p_a; if (st == 0 && local == 0) p_first = d; else p_wait += d; }
-#endif
                     fence_proxy_async();   // cp.async (generic proxy) writes -> tcgen05.mma (async proxy) reads
                     tc_fence_after();
                     const uint32_t a_tile = stage_base + (uint32_t)(RB * s) * STAGE_BYTES;
@@ -284,13 +269,6 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
                 if (elect_one_sync()) umma_commit(smem_u32(&tail->accum_full[buf]));
                 __syncwarp();
             }
-#ifdef SV_PROFILE
-            if (lane == 0) {
-                g_prof[blockIdx.x * 8 + 0] = clock64() - p_t0;     // whole MMA loop
-                g_prof[blockIdx.x * 8 + 1] = p_wait;               // waiting for operands (all steps but the first)
-                g_prof[blockIdx.x * 8 + 2] = p_first;              // waiting for the first operands
-            }
-#endif
         }
     } else {
         // ------------------------------------------------------------------ epilogue (warps 5..8)
@@ -647,7 +625,7 @@ static int launch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaStre
     if (nstage < 2)
         return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core conv: not enough shared memory for BN=%d kk=%d", BN, p.kk);
     // rounds of two buffers once three rounds fit (narrow column blocks); otherwise one buffer per round
-    const bool two = nstage >= 6 || (getenv("SVTAD_X_RB2") != nullptr && nstage >= 4);
+    const bool two = nstage >= 6;
     if (two) nstage &= ~1;
     const size_t smem = 1024 + nstage * stage + extra;
     auto kern = two ? conv_hybrid_kernel<BN, DGRAD, 2> : conv_hybrid_kernel<BN, DGRAD, 1>;
@@ -676,11 +654,6 @@ static int dispatch_conv_hybrid(const ConvArgs& p, const int32_t* status, cudaSt
     return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core conv: no column block for width %d", cn);
 }
 
-#ifdef SV_PROFILE
-extern "C" int svtad_prof_read(long long* out) {
-    return cudaMemcpyFromSymbol(out, g_prof, sizeof(long long) * 148 * 8) == cudaSuccess ? 0 : 1;
-}
-#endif
 
 int hybrid_fwd(const ConvArgs& p, cudaStream_t s) { return dispatch_conv_hybrid<false>(p, nullptr, s); }
 int hybrid_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s) { return dispatch_conv_hybrid<true>(p, status, s); }

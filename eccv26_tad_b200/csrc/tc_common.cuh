@@ -287,10 +287,7 @@ struct WgradPlan {
 };
 WgradPlan tc_wgrad_plan(int64_t n, int cin, int cout, int kk);
 size_t tc_wgrad_plan_ws_bytes(int64_t n, int cin, int cout, int kk);
-WgradPlan tc_wgrad_plan_with(int64_t n, int cin, int cout, int kk, int bn, long other_items, int other_steps);
-// one-launch backward (conv_tc_multi.cu)
-bool multi_bwd_supported(int64_t n, int cin, int cout, int kk);
-WgradPlan multi_bwd_plan(int64_t n, int cin, int cout, int kk);
+
 // fixed-order reduction of per-split fp32 partials into the 16-bit gradient tensors
 int tc_wgrad_reduce_launch(const float* ws_w, int splits, const float* ws_b, int splits_b, void* gw, void* gb,
                            long n_w, int cout, int fp16, cudaStream_t s);

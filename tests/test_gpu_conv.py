@@ -29,7 +29,6 @@ def _no_forced_path(monkeypatch):
     monkeypatch.delenv("SVTAD_TC_BN", raising=False)
     monkeypatch.delenv("SVTAD_TC_WGRAD_CLUSTER", raising=False)
     monkeypatch.delenv("SVTAD_TC_IMPL", raising=False)
-    monkeypatch.delenv("SVTAD_TC_FUSED_BWD", raising=False)
     yield
     assert _ops().device_error() == 0, "a bounded wait inside a tensor-core kernel gave up"
 
@@ -437,10 +436,10 @@ def _fused_bwd(table, x, w, gy, tpb=0):
     (768, 3, torch.bfloat16, (1, 6, 0.3)),       # three column blocks per row tile and per block pair
     (192, 3, torch.bfloat16, (1, 1, 0.02)),      # 4 rows: one tile, one split
 ])
-def test_one_launch_backward_against_oracle(C, ks, dtype, shape):
-    """The backward of a layer as ONE launch over a work list (input-gradient tiles + weight-gradient items), taken
-    when the caller vouches for a symmetric table: both gradients against the oracle, the input gradient bitwise
-    equal to the stand-alone kernel's, and bitwise repeatable."""
+def test_one_call_backward_symmetric_tables_against_oracle(C, ks, dtype, shape):
+    """The one-call backward without a status word (the caller vouches for a symmetric table: no validation pass, no
+    scatter-form launches): both gradients against the oracle, the input gradient bitwise equal to the stand-alone
+    kernel's, and bitwise repeatable."""
     ops = _ops()
     B, T, keep = shape
     _, _, table = make_table(B, T, 14, 14, keep, ks, 55)
@@ -460,7 +459,7 @@ def test_one_launch_backward_against_oracle(C, ks, dtype, shape):
             assert torch.equal(u, v)
 
 
-def test_one_launch_backward_ragged_rows_and_batch_local_indices():
+def test_one_call_backward_symmetric_ragged_rows_and_batch_local_indices():
     for n in (1, 129, 1000):
         table = _chain_table(n)
         x, w, b, gy = make_conv_inputs(n, 192, 192, 3, torch.bfloat16, n, bias="random")
