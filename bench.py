@@ -11,7 +11,7 @@ forward, input gradient, weight + bias gradient for all three keep rates on one 
 (29 920 retained tokens per GPU).  Data are synthetic and seeded; there is no dataset behind
 this op.  With N > 1 every rank owns its own batch (weak scaling, sharded by clip) and the
 weight / bias gradients are all-reduced over NCCL every step, as data-parallel training does
-(SVTAD_BENCH_ALLREDUCE=symm: bucket in symmetric memory, two-shot all-reduce over NVLink peer loads).
+(by this library's own two-shot exchange over NVLink peer memory; SVTAD_BENCH_ALLREDUCE=nccl: NCCL all-reduce).
 
 Numbers on the JSON line
   value        tokens/s over all ranks with inputs already resident in HBM; every step reads a
@@ -295,15 +295,15 @@ def main():
     # the way DDP buckets the adapters' gradients (reference: src/eccv26_tad.py:288-300, 25 MB buckets)
     per_layer = KK * C * C + C
     n_grads = len(KEEPS) * per_layer
-    # N > 1: NCCL all-reduce of the bucket.  SVTAD_BENCH_ALLREDUCE=symm puts the bucket in symmetric memory and
-    # sums it with a two-shot all-reduce over NVLink peer loads instead (measured 0.1714 vs 0.1914 ms per step on
-    # 8 GPUs); it stays opt-in because it has been run far less often than the NCCL path.
+    # N > 1: the bucket lives in peer-mapped memory and is summed by svtad_allreduce_sum (two-shot exchange by plain
+    # loads and stores over NVLink, bounded waits); SVTAD_BENCH_ALLREDUCE=nccl keeps an ordinary tensor + NCCL.
+    # The ranks decide together (one collective vote) before any set-up call; a "no" puts all of them on NCCL.
     from eccv26_tad_b200.distributed import GradBucket
     bucket = GradBucket(n_grads, torch.bfloat16, dev,
-                        allow_symmetric=os.environ.get("SVTAD_BENCH_ALLREDUCE", "nccl") == "symm")
+                        exchange="collective" if os.environ.get("SVTAD_BENCH_ALLREDUCE", "peer") == "nccl" else "peer")
     grads, allreduce_kind = bucket.buffer, bucket.kind
     if world > 1 and bucket.kind == "nccl" and hasattr(bucket, "fallback_reason"):
-        sys.stderr.write(f"[bench] symmetric-memory all-reduce unavailable ({bucket.fallback_reason}); using NCCL\n")
+        sys.stderr.write(f"[bench] peer-memory all-reduce unavailable ({bucket.fallback_reason}); using NCCL\n")
     gw_bufs = [grads[i * per_layer:i * per_layer + KK * C * C] for i in range(len(KEEPS))]
     gb_bufs = [grads[i * per_layer + KK * C * C:(i + 1) * per_layer] for i in range(len(KEEPS))]
     gw_buf, gb_buf = gw_bufs[0], gb_bufs[0]

@@ -183,16 +183,6 @@ WgradPlan tc_wgrad_plan(int64_t n, int cin, int cout, int kk) {
     }
     const char* e = getenv("SVTAD_TC_WGRAD_SPLITS");
     if (e != nullptr && *e && atoi(e) > 0) s = atoi(e) < max_by_rows ? atoi(e) : max_by_rows;
-    // SVTAD_TC_WGRAD_CLUSTER=1: up to a dozen splits are capped at 8 (the portable cluster size) and reduced
-    // through distributed shared memory instead of a workspace round trip.  Off by default: on B200 it wins at
-    // 3 200 rows (18.5 -> 15.7 us) but 14 x 8 = 112 CTAs leave 36 SMs idle and lose at 9 440 / 17 280 rows.
-    const char* c = getenv("SVTAD_TC_WGRAD_CLUSTER");
-    const bool allow_cluster = (c != nullptr && c[0] == '1');
-    pl.cluster = 0;
-    if (allow_cluster && s <= 12) {
-        if (s > 8) s = 8;
-        pl.cluster = 1;
-    }
     long tps = ((n + s - 1) / s + STAGE_K - 1) / STAGE_K * STAGE_K;
     pl.tokens_per_split = tps;
     pl.splits = (int)((n + tps - 1) / tps);

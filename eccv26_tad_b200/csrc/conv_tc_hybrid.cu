@@ -316,13 +316,10 @@ conv_hybrid_kernel(const __grid_constant__ CUtensorMap map_w, const uint16_t* __
 // ---------------------------------------------------------------------------------------------
 // wgrad
 // ---------------------------------------------------------------------------------------------
-// CLUSTER = true: the CTAs of one block pair (one per token split) form a thread-block cluster and sum their
-// partial tiles through distributed shared memory in a fixed order, writing gw / gb directly; no workspace.
-template <int BN, bool CLUSTER>
+template <int BN>
 __global__ void __launch_bounds__(HY_THREADS, 1)
 wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* __restrict__ x,
                     const int32_t* __restrict__ nbr, float* __restrict__ ws_w, float* __restrict__ ws_b,
-                    uint16_t* __restrict__ gw, uint16_t* __restrict__ gb,
                     long n, int cin, int cout, int kk, int tpb, long tokens_per_split, int n_nblk,
                     int nstage, int fp16, int ones_block, int* __restrict__ err) {
     constexpr int B_TILE_BYTES = b_tile_bytes_for(BN);
@@ -521,9 +518,6 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
             } else if (ones_here && q == 2 && lane == 0 && ws_b != nullptr) {
                 dstrow = ws_b + (long)blockIdx.y * cout + n0;
             }
-            if (CLUSTER) dstrow = nullptr;
-            // cluster mode: the tile is parked in this CTA's (now idle) stage ring, row stride BN + 4 floats
-            float* stage_row = reinterpret_cast<float*>(smem) + (q * 32 + lane) * (BN + 4);
             constexpr int NC = BN / 32;
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
             uint32_t va[32], vb[32];
@@ -538,11 +532,7 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
 #pragma unroll
                     for (int j = 0; j < 32; ++j) v[j] = 0u;
                 }
-                if (CLUSTER) {
-                    uint4* dst = reinterpret_cast<uint4*>(stage_row + c * 32);
-#pragma unroll
-                    for (int g = 0; g < 8; ++g) dst[g] = make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-                } else if (dstrow != nullptr) {
+                if (dstrow != nullptr) {
                     // 32 bytes (one whole sector) per store: the workspace is 256-byte aligned, rows are cout * 4 bytes
                     float* dst = dstrow + c * 32;
 #pragma unroll
@@ -553,49 +543,6 @@ wgrad_hybrid_kernel(const __grid_constant__ CUtensorMap map_gy, const uint16_t* 
     }
     tc_fence_before();
     __syncthreads();
-    if (CLUSTER) {
-        // every thread of every CTA of the cluster gets here, also after an aborted wait
-        uint32_t rank, csize;
-        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-        asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(csize));
-        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-        // this CTA sums rows [r_lo, r_hi) of the tile over all splits, split 0 first
-        const int rows_per = (TILE_M + (int)csize - 1) / (int)csize;
-        const int r_lo = (int)rank * rows_per;
-        const int r_hi = r_lo + rows_per < TILE_M ? r_lo + rows_per : TILE_M;
-        constexpr int G = BN / 4;
-        const uint32_t local_base = smem_u32(smem);
-        for (int g = tid; g < (r_hi - r_lo) * G; g += HY_THREADS) {
-            const int row = r_lo + g / G, c4 = g % G;
-            const int blk = pair * 2 + (row >> 6);
-            uint16_t* dst = nullptr;
-            if (blk < nblocks) {
-                const long grow = (long)(blk / cblocks) * cin + (blk % cblocks) * 64 + (row & 63);
-                dst = gw + grow * cout + n0 + c4 * 4;
-            } else if (ones_here && row == 64 && gb != nullptr) {
-                dst = gb + n0 + c4 * 4;
-            }
-            if (dst == nullptr) continue;
-            const uint32_t off = (uint32_t)(row * (BN + 4) + c4 * 4) * 4u;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (uint32_t p = 0; p < csize; ++p) {
-                uint32_t peer;
-                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(local_base + off), "r"(p));
-                float4 v;
-                asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
-                             : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(peer) : "memory");
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-            }
-            uint2 o;
-            o.x = pack2(acc.x, acc.y, fp16 != 0);
-            o.y = pack2(acc.z, acc.w, fp16 != 0);
-            *reinterpret_cast<uint2*>(dst) = o;
-        }
-        // nobody leaves while a peer may still read its shared memory
-        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-    }
     if (warp == 4) {
         __syncwarp();
         tc_fence_after();
@@ -659,8 +606,7 @@ int hybrid_fwd(const ConvArgs& p, cudaStream_t s) { return dispatch_conv_hybrid<
 int hybrid_dgrad(const ConvArgs& p, const int32_t* status, cudaStream_t s) { return dispatch_conv_hybrid<true>(p, status, s); }
 
 template <int BN>
-static int launch_wgrad_hybrid(const void* gy, const void* x, const int32_t* nbr, float* ws_w, float* ws_b,
-                               void* gw, void* gb, int64_t n, int cin, int cout, int kk, int tpb, int fp16,
+static int launch_wgrad_hybrid(const void* gy, const void* x, const int32_t* nbr, float* ws_w, float* ws_b, int64_t n, int cin, int cout, int kk, int tpb, int fp16,
                                const WgradPlan& pl, cudaStream_t s) {
     CUtensorMap map_gy;
     {
@@ -676,32 +622,10 @@ static int launch_wgrad_hybrid(const void* gy, const void* x, const int32_t* nbr
     if (nstage < 2)
         return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core wgrad: not enough shared memory for BN=%d kk=%d", BN, kk);
     const size_t smem = 1024 + nstage * stage + extra;
-    const bool cluster = pl.cluster && (size_t)TILE_M * (BN + 4) * sizeof(float) <= nstage * stage;
     dim3 grid((unsigned)(pl.n_pairs * pl.n_nblk), (unsigned)pl.splits);
-    if (cluster) {
-        auto kern = wgrad_hybrid_kernel<BN, true>;
-        { int rc_s = tc_ensure_smem(reinterpret_cast<const void*>(kern), smem); if (rc_s) return rc_s; }
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = grid;
-        cfg.blockDim = dim3(HY_THREADS);
-        cfg.dynamicSmemBytes = smem;
-        cfg.stream = s;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 1;
-        attr[0].val.clusterDim.y = (unsigned)pl.splits;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        SV_CUDA(cudaLaunchKernelEx(&cfg, kern, map_gy, (const uint16_t*)x, nbr, (float*)nullptr, (float*)nullptr,
-                                   (uint16_t*)gw, (uint16_t*)gb, (long)n, cin, cout, kk, tpb, pl.tokens_per_split,
-                                   pl.n_nblk, nstage, fp16, pl.ones_block, tc_error_ptr()));
-        return SVTAD_OK;
-    }
-    auto kern = wgrad_hybrid_kernel<BN, false>;
+    auto kern = wgrad_hybrid_kernel<BN>;
     { int rc_s = tc_ensure_smem(reinterpret_cast<const void*>(kern), smem); if (rc_s) return rc_s; }
-    SV_CUDA(tc_launch(kern, grid, dim3(HY_THREADS), smem, s, map_gy, (const uint16_t*)x, nbr, ws_w, ws_b,
-                      (uint16_t*)nullptr, (uint16_t*)nullptr, (long)n, cin, cout, kk, tpb, pl.tokens_per_split,
+    SV_CUDA(tc_launch(kern, grid, dim3(HY_THREADS), smem, s, map_gy, (const uint16_t*)x, nbr, ws_w, ws_b, (long)n, cin, cout, kk, tpb, pl.tokens_per_split,
                       pl.n_nblk, nstage, fp16, pl.ones_block, tc_error_ptr()));
     return SVTAD_OK;
 }
@@ -718,26 +642,15 @@ int hybrid_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw, vo
     float* ws_b = reinterpret_cast<float*>(static_cast<char*>(ws) + align_up((size_t)pl.splits * n_w * sizeof(float), 256));
     const bool bias_in_kernel = gb != nullptr && pl.ones_block;
     float* kb = bias_in_kernel ? ws_b : nullptr;
-    void* kgb = bias_in_kernel ? gb : nullptr;
     int rc;
     switch (pl.bn) {
-        case 64: rc = launch_wgrad_hybrid<64>(gy, x, nbr, ws_w, kb, gw, kgb, n, cin, cout, kk, tpb, fp16, pl, s); break;
-        case 128: rc = launch_wgrad_hybrid<128>(gy, x, nbr, ws_w, kb, gw, kgb, n, cin, cout, kk, tpb, fp16, pl, s); break;
-        case 192: rc = launch_wgrad_hybrid<192>(gy, x, nbr, ws_w, kb, gw, kgb, n, cin, cout, kk, tpb, fp16, pl, s); break;
-        case 256: rc = launch_wgrad_hybrid<256>(gy, x, nbr, ws_w, kb, gw, kgb, n, cin, cout, kk, tpb, fp16, pl, s); break;
+        case 64: rc = launch_wgrad_hybrid<64>(gy, x, nbr, ws_w, kb, n, cin, cout, kk, tpb, fp16, pl, s); break;
+        case 128: rc = launch_wgrad_hybrid<128>(gy, x, nbr, ws_w, kb, n, cin, cout, kk, tpb, fp16, pl, s); break;
+        case 192: rc = launch_wgrad_hybrid<192>(gy, x, nbr, ws_w, kb, n, cin, cout, kk, tpb, fp16, pl, s); break;
+        case 256: rc = launch_wgrad_hybrid<256>(gy, x, nbr, ws_w, kb, n, cin, cout, kk, tpb, fp16, pl, s); break;
         default: return set_error(SVTAD_ERR_UNSUPPORTED, "tensor-core wgrad: no column block for width %d", cout);
     }
     if (rc) return rc;
-    if (pl.cluster) {
-        // gw (and gb when the all-ones block exists) are final; a bias gradient without that block takes its own pass
-        if (gb != nullptr && !bias_in_kernel) {
-            int sb = bias_splits_for(n);
-            rc = bias_partial_launch(gy, ws_b, n, cout, dtype, sb, s);
-            if (rc) return rc;
-            return tc_wgrad_reduce_launch(ws_w, 0, ws_b, sb, nullptr, gb, 0, cout, fp16, s);
-        }
-        return SVTAD_OK;
-    }
     int splits_b = 0;
     if (gb != nullptr) {
         if (bias_in_kernel) {

@@ -282,7 +282,6 @@ int tc_make_map_sw(CUtensorMap* map, int rank, const void* base, const uint64_t*
 int tc_pick_bn(int cn, long m_tiles);
 struct WgradPlan {
     int bn, n_nblk, n_pairs, splits, ones_block;
-    int cluster;   // the splits of a block pair form one thread-block cluster (splits <= 8) and reduce on chip
     long tokens_per_split;
 };
 WgradPlan tc_wgrad_plan(int64_t n, int cin, int cout, int kk);

@@ -184,8 +184,35 @@ int svtad_conv_wgrad_static(const void* gy, const void* x, const int32_t* nbr, v
                             void* stream);
 
 /*
+ * Sum of a 16-bit gradient bucket over the `world` ranks (GPUs) of one node, in place, by a two-shot exchange
+ * over peer-mapped memory: rank r adds up slice r of all ranks' buckets (plain loads over NVLink, rank order
+ * 0..world-1, fp32, one rounding) and stores the result into slice r of every rank's bucket.  Replaces the
+ * bucket all-reduce torch DDP issues for the adapters' gradients in the reference's training loop
+ * (src/eccv26_tad.py:288-300); there the collective is NCCL's.
+ *   peer_bufs   HOST array of `world` device pointers: rank p's bucket as THIS rank can address it (its own
+ *               bucket at index `rank`).  The caller maps the memory (CUDA IPC, cuMem, torch symmetric memory).
+ *   n_elems     elements of the bucket, a multiple of 8 * world (pad with zeros)
+ *   flag_offset_bytes   where, behind the bucket in the same allocation, svtad_allreduce_flag_bytes() bytes of
+ *               flag words live; they must be zero before the first call and belong to this function afterwards
+ *   epoch       svtad_allreduce_epoch_bytes() bytes of LOCAL device memory, zero before the first call
+ *   wait_limit_cycles   how long a CTA waits for a peer (SM clock cycles; 0 = about one second).  When the limit
+ *               runs out the CTA records code 71 / 72 in the device error word (svtad_device_error), leaves the
+ *               bucket as it is and returns; nothing hangs and the context stays usable.
+ * Every rank must make the same sequence of calls.  The launch can be captured into a CUDA graph (the call
+ * number that the flags carry is kept on the device).  No multicast, no NVLS.
+ * svtad_allreduce_sum_emulated runs all ranks' parts in one cooperative launch on the current device (`bufs` are
+ * then `world` local buffers, `epochs` holds world * 32 words): for tests on machines with fewer GPUs than ranks.
+ */
+size_t svtad_allreduce_flag_bytes(void);
+size_t svtad_allreduce_epoch_bytes(void);
+int svtad_allreduce_sum(void* const* peer_bufs, int rank, int world, int64_t n_elems, int dtype,
+                        size_t flag_offset_bytes, void* epoch, int64_t wait_limit_cycles, void* stream);
+int svtad_allreduce_sum_emulated(void* const* bufs, int world, int64_t n_elems, int dtype,
+                                 size_t flag_offset_bytes, void* epochs, int64_t wait_limit_cycles, void* stream);
+
+/*
  * Reads (and clears) the device-side error word of the current device: non-zero means a bounded
- * wait inside a tensor-core kernel gave up and that launch's output is invalid.  Synchronises
+ * wait inside a kernel gave up and that launch's output is invalid.  Synchronises
  * the device.  No reference counterpart.
  */
 int svtad_device_error(int32_t* code_out);

@@ -27,7 +27,6 @@ def _ops():
 def _no_forced_path(monkeypatch):
     monkeypatch.delenv("SVTAD_FORCE_PATH", raising=False)
     monkeypatch.delenv("SVTAD_TC_BN", raising=False)
-    monkeypatch.delenv("SVTAD_TC_WGRAD_CLUSTER", raising=False)
     monkeypatch.delenv("SVTAD_TC_IMPL", raising=False)
     yield
     assert _ops().device_error() == 0, "a bounded wait inside a tensor-core kernel gave up"
@@ -143,18 +142,6 @@ def test_cta_pair_kernels_ragged_rows_and_batch_local_indices(monkeypatch):
     x, w, b, gy = make_conv_inputs(n, 128, 128, 3, torch.bfloat16, 9, bias="random")
     outs = _run_all(local, x, w, b, gy, tpb=tpb)
     _check_all(local, x, w, b, gy, outs, 2e-2, tpb=tpb)
-
-
-def test_wgrad_cluster_reduction_variant(monkeypatch):
-    """Optional wgrad form: the splits of a block pair reduce through distributed shared memory."""
-    monkeypatch.setenv("SVTAD_TC_WGRAD_CLUSTER", "1")
-    for B, T, keep in [(2, 80, 0.1), (1, 30, 0.55), (1, 1, 0.3)]:
-        _, _, table = make_table(B, T, 14, 14, keep, 3, 123)
-        n = table.shape[0]
-        x, w, b, gy = make_conv_inputs(n, 192, 192, 3, torch.bfloat16, 123, bias="random")
-        outs = _run_all(table, x, w, b, gy)
-        _check_all(table, x, w, b, gy, outs, 2e-2)
-    monkeypatch.setenv("SVTAD_TC_WGRAD_CLUSTER", "0")
 
 
 def test_tc_and_simt_agree_tightly(monkeypatch):

@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from eccv26_tad_b200.distributed import GradBucket, allreduce_weight_grads, shard_clips
+from eccv26_tad_b200.distributed import GradBucket, allreduce_weight_grads, padded_numel, shard_clips, slice_bounds
 from oracle import conv as oconv
 from oracle import table as otab
 
@@ -49,6 +49,13 @@ def _worker(rank, world, port, out):
         flat = bucket.all_reduce()
         assert bucket.kind == "gloo"
         assert torch.equal(flat[:gw.size].view(gw.shape), gw_t) and torch.equal(flat[gw.size:], gb_t)
+        # asking for the peer-memory exchange where it cannot work (CPU ranks): the decision is taken once for all
+        # ranks by a collective BEFORE any set-up call, so both ranks land on the collective path together
+        b16 = GradBucket(gw.size + gb.size, torch.bfloat16, "cpu", exchange="peer")
+        assert b16.kind == "gloo" and "not every rank" in b16.fallback_reason
+        b16.buffer.copy_(torch.arange(b16.numel, dtype=torch.float32).remainder(7).to(torch.bfloat16) * (rank + 1))
+        s16 = b16.all_reduce()
+        assert torch.equal(s16.float(), torch.arange(b16.numel, dtype=torch.float32).remainder(7) * 3)
         out[rank] = dict(lo=lo, hi=hi, y=y, gx=gx, gw=gw_t.numpy().copy(), gb=gb_t.numpy().copy())
     finally:
         dist.destroy_process_group()
@@ -75,6 +82,24 @@ def test_two_gloo_ranks_match_single_rank():
         np.testing.assert_allclose(o["gb"], gb, rtol=1e-12, atol=1e-12)
         covered += o["hi"] - o["lo"]
     assert covered == table.shape[0]
+
+
+def test_two_shot_slices_partition_the_bucket():
+    """The slices / CTA shares of the peer-memory exchange cover the bucket exactly once, in whole 16-byte vectors."""
+    for numel, world, ctas in [(995904, 8, 32), (995904, 2, 32), (1024, 4, 1), (64 * 3, 3, 5), (padded_numel(1000, 8), 8, 7)]:
+        seen = np.zeros(numel, dtype=np.int32)
+        for r in range(world):
+            (lo, hi), shares = slice_bounds(numel, r, world, ctas)
+            assert lo % 8 == 0 and hi % 8 == 0 and hi - lo == numel // world
+            assert shares[0][0] == lo and max(b for _, b in shares) == hi
+            for a, b in shares:
+                assert a % 8 == 0 and b % 8 == 0 and lo <= a <= b <= hi
+                seen[a:b] += 1
+        assert (seen == 1).all()
+    assert padded_numel(995904, 8) % (64 * 8) == 0 and padded_numel(995904, 8) - 995904 < 64 * 8
+    import pytest
+    with pytest.raises(ValueError):
+        slice_bounds(100, 0, 8)
 
 
 def test_shard_clips_partitions():
