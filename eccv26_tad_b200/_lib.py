@@ -33,7 +33,7 @@ SIGNATURES = {
     "svtad_conv_bwd": (c_int, [c_p, c_p, c_p, c_p, c_p, c_p, c_p, c_i64, c_int, c_int, c_int, c_int, c_int, c_p, c_p, c_sz, c_p]),
     "svtad_static_workspace_bytes": (c_sz, []),
     "svtad_conv_wgrad_static": (c_int, [c_p, c_p, c_p, c_p, c_p, c_i64, c_int, c_int, c_int, c_int, c_int, c_p]),
-    "svtad_allreduce_flag_bytes": (c_sz, []),
+    "svtad_allreduce_stage_bytes": (c_sz, [c_i64]),
     "svtad_allreduce_epoch_bytes": (c_sz, []),
     "svtad_allreduce_sum": (c_int, [ctypes.POINTER(c_p), c_int, c_int, c_i64, c_int, c_sz, c_p, c_i64, c_p]),
     "svtad_allreduce_sum_emulated": (c_int, [ctypes.POINTER(c_p), c_int, c_i64, c_int, c_sz, c_p, c_i64, c_p]),

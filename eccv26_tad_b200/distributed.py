@@ -20,22 +20,14 @@ def shard_clips(n_clips, rank, world_size):
     return range(start, start + base + (1 if rank < extra else 0))
 
 
-def slice_bounds(numel, rank, world_size, n_ctas=1):
+def slice_bounds(numel, rank, world_size):
     """The part of a bucket of ``numel`` 16-bit elements that ``rank`` sums in the two-shot exchange, as
-    ``(first, last)`` element indices, and the share of each of its ``n_ctas`` CTAs as a list of such pairs.
-    Mirrors the kernel (csrc/allreduce.cu): the bucket is cut into ``world_size`` slices of whole 16-byte vectors,
-    a slice into ``n_ctas`` runs of ``ceil(slice / n_ctas)`` vectors."""
+    ``(first, last)`` element indices.  Mirrors the kernel (csrc/allreduce.cu): the bucket is cut into
+    ``world_size`` slices of whole 16-byte units (8 elements)."""
     if numel % (8 * world_size):
         raise ValueError(f"a bucket of {numel} elements is not a multiple of 8 * {world_size}: pad it")
-    per_rank = numel // 8 // world_size
-    per_cta = -(-per_rank // n_ctas)
-    lo = rank * per_rank
-    shares = []
-    for c in range(n_ctas):
-        a = min(lo + c * per_cta, lo + per_rank)
-        b = min(a + per_cta, lo + per_rank)
-        shares.append((a * 8, b * 8))
-    return (lo * 8, (lo + per_rank) * 8), shares
+    per_rank = numel // world_size
+    return rank * per_rank, (rank + 1) * per_rank
 
 
 def padded_numel(numel, world_size):
@@ -90,7 +82,7 @@ class GradBucket:
 
     ``exchange="peer"``: the bucket is placed in memory that every rank of the node maps (torch's symmetric-memory
     allocator does the allocation and the handle exchange; multicast is not used) and summed by this library's own
-    two-shot kernel (``svtad_allreduce_sum``: plain loads and stores over NVLink, bounded waits).  Whether that is
+    two-shot kernel (``svtad_allreduce_sum``: plain stores over NVLink that carry their own flags, bounded waits).  Whether that is
     possible is decided ONCE FOR ALL RANKS before any symmetric-memory call: every rank evaluates its own
     capabilities on the host and the minimum over the ranks is taken with one ordinary all-reduce on the default
     path.  If any rank says no, every rank uses the collective path.  After a unanimous yes, a failure of the
@@ -131,10 +123,10 @@ class GradBucket:
         lib = _lib.load()
         pg = group if group is not None else dist.group.WORLD
         n_pad = padded_numel(numel, world)
-        flag_elems = lib.svtad_allreduce_flag_bytes() // 2
-        buf = symm_mem.empty(n_pad + flag_elems, dtype=dtype, device=device)
+        stage_elems = lib.svtad_allreduce_stage_bytes(n_pad) // 2
+        buf = symm_mem.empty(n_pad + stage_elems, dtype=dtype, device=device)
         hdl = symm_mem.rendezvous(buf, pg)
-        buf.zero_()                                   # flags (and padding) start at zero on every rank ...
+        buf.zero_()                                   # staging areas (and padding) start at zero on every rank ...
         torch.cuda.synchronize(device)
         dist.barrier(group=group)                     # ... before any rank's first exchange can write into them
         ptrs = [int(p) for p in hdl.buffer_ptrs]
@@ -146,7 +138,7 @@ class GradBucket:
             "rank": int(hdl.rank),
             "world": world,
             "n_pad": n_pad,
-            "flag_off": n_pad * 2,
+            "stage_off": n_pad * 2,
             "epoch": torch.zeros(lib.svtad_allreduce_epoch_bytes() // 4, dtype=torch.int32, device=device),
             "dtype": _lib.BF16 if dtype == torch.bfloat16 else _lib.F16,
             "limit": int(os.environ.get("SVTAD_ALLREDUCE_WAIT_CYCLES", "0")),
@@ -168,7 +160,7 @@ class GradBucket:
             stream = torch.cuda.current_stream(self.buffer.device).cuda_stream
             with torch.cuda.device(self.buffer.device):
                 _lib.check(_lib.load().svtad_allreduce_sum(p["ptrs"], p["rank"], p["world"], p["n_pad"], p["dtype"],
-                                                           p["flag_off"], p["epoch"].data_ptr(), p["limit"], stream))
+                                                           p["stage_off"], p["epoch"].data_ptr(), p["limit"], stream))
         elif self.kind != "none":
             dist.all_reduce(self.buffer, op=dist.ReduceOp.SUM, group=self.group)
         return self.buffer[:self.numel]

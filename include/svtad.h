@@ -185,15 +185,18 @@ int svtad_conv_wgrad_static(const void* gy, const void* x, const int32_t* nbr, v
 
 /*
  * Sum of a 16-bit gradient bucket over the `world` ranks (GPUs) of one node, in place, by a two-shot exchange
- * over peer-mapped memory: rank r adds up slice r of all ranks' buckets (plain loads over NVLink, rank order
- * 0..world-1, fp32, one rounding) and stores the result into slice r of every rank's bucket.  Replaces the
+ * over peer-mapped memory: every rank pushes its copy of slice p to rank p, rank p adds the copies up (rank order
+ * 0..world-1, fp32, one rounding: all ranks get bit-identical sums) and pushes the result back to everyone.  What
+ * crosses NVLink are plain 16-byte stores in which every 8 bytes carry their own flag word (the number of the
+ * call), so no phase waits for a system fence or a separate flag.  Replaces the
  * bucket all-reduce torch DDP issues for the adapters' gradients in the reference's training loop
  * (src/eccv26_tad.py:288-300); there the collective is NCCL's.
- *   peer_bufs   HOST array of `world` device pointers: rank p's bucket as THIS rank can address it (its own
- *               bucket at index `rank`).  The caller maps the memory (CUDA IPC, cuMem, torch symmetric memory).
- *   n_elems     elements of the bucket, a multiple of 8 * world (pad with zeros)
- *   flag_offset_bytes   where, behind the bucket in the same allocation, svtad_allreduce_flag_bytes() bytes of
- *               flag words live; they must be zero before the first call and belong to this function afterwards
+ *   peer_bufs   HOST array of `world` device pointers: rank p's allocation as THIS rank can address it (its own
+ *               at index `rank`).  The caller maps the memory (CUDA IPC, cuMem, torch symmetric memory).
+ *   n_elems     elements of the bucket (the start of the allocation), a multiple of 8 * world (pad with zeros)
+ *   stage_offset_bytes   where, behind the bucket in the same allocation, svtad_allreduce_stage_bytes(n_elems)
+ *               bytes of staging space live; they must be zero before the first call and belong to this function
+ *               afterwards
  *   epoch       svtad_allreduce_epoch_bytes() bytes of LOCAL device memory, zero before the first call
  *   wait_limit_cycles   how long a CTA waits for a peer (SM clock cycles; 0 = about one second).  When the limit
  *               runs out the CTA records code 71 / 72 in the device error word (svtad_device_error), leaves the
@@ -201,14 +204,14 @@ int svtad_conv_wgrad_static(const void* gy, const void* x, const int32_t* nbr, v
  * Every rank must make the same sequence of calls.  The launch can be captured into a CUDA graph (the call
  * number that the flags carry is kept on the device).  No multicast, no NVLS.
  * svtad_allreduce_sum_emulated runs all ranks' parts in one cooperative launch on the current device (`bufs` are
- * then `world` local buffers, `epochs` holds world * 32 words): for tests on machines with fewer GPUs than ranks.
+ * then `world` local buffers, `epochs` holds svtad_allreduce_epoch_bytes()): for tests on machines with fewer GPUs than ranks.
  */
-size_t svtad_allreduce_flag_bytes(void);
+size_t svtad_allreduce_stage_bytes(int64_t n_elems);
 size_t svtad_allreduce_epoch_bytes(void);
 int svtad_allreduce_sum(void* const* peer_bufs, int rank, int world, int64_t n_elems, int dtype,
-                        size_t flag_offset_bytes, void* epoch, int64_t wait_limit_cycles, void* stream);
+                        size_t stage_offset_bytes, void* epoch, int64_t wait_limit_cycles, void* stream);
 int svtad_allreduce_sum_emulated(void* const* bufs, int world, int64_t n_elems, int dtype,
-                                 size_t flag_offset_bytes, void* epochs, int64_t wait_limit_cycles, void* stream);
+                                 size_t stage_offset_bytes, void* epochs, int64_t wait_limit_cycles, void* stream);
 
 /*
  * Reads (and clears) the device-side error word of the current device: non-zero means a bounded

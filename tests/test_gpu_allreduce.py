@@ -18,7 +18,7 @@ def _setup(world, numel, dtype, seed):
     from eccv26_tad_b200.distributed import padded_numel
     lib = _lib.load()
     n_pad = padded_numel(numel, world)
-    flag_elems = lib.svtad_allreduce_flag_bytes() // 2
+    flag_elems = lib.svtad_allreduce_stage_bytes(n_pad) // 2
     g = torch.Generator().manual_seed(seed)
     bufs, vals = [], []
     for r in range(world):
@@ -63,7 +63,7 @@ def test_emulated_ranks_sum_bit_exactly_and_repeatedly(world, numel, dtype):
 
 def test_wait_for_an_absent_peer_runs_out_and_reports():
     """Rank 0 of a two-rank exchange whose rank 1 never launches: the flag that nothing sets makes the first wait run
-    out after the (short) limit; the kernel reports code 71, leaves the bucket alone, and the GPU keeps working."""
+    out after the (short) limit; the kernel reports code 71, leaves the bucket as it was, and the GPU keeps working."""
     from eccv26_tad_b200 import ops
     lib, _lib, n_pad, bufs, vals = _setup(2, 4096, torch.bfloat16, 9)
     epoch = torch.zeros(lib.svtad_allreduce_epoch_bytes() // 4, dtype=torch.int32, device="cuda")
@@ -79,7 +79,7 @@ def test_wait_for_an_absent_peer_runs_out_and_reports():
     assert int(epoch.abs().sum()) == 0                   # the call did not count
     # the context is intact: an ordinary exchange (all ranks emulated) still works afterwards
     for b in bufs:
-        b[4096:].zero_()
+        b[n_pad:].zero_()
     epochs = torch.zeros(lib.svtad_allreduce_epoch_bytes() // 4, dtype=torch.int32, device="cuda")
     _lib.check(lib.svtad_allreduce_sum_emulated(ptrs, 2, n_pad, _lib.BF16, n_pad * 2, epochs.data_ptr(), 0,
                                                 torch.cuda.current_stream().cuda_stream))
@@ -91,11 +91,11 @@ def test_wait_for_an_absent_peer_runs_out_and_reports():
 def test_bad_arguments_are_refused_on_the_host():
     from eccv26_tad_b200 import _lib
     lib = _lib.load()
-    buf = torch.zeros(8192, dtype=torch.bfloat16, device="cuda")
+    buf = torch.zeros(16384, dtype=torch.bfloat16, device="cuda")
     ptrs = (ctypes.c_void_p * 2)(buf.data_ptr(), buf.data_ptr())
-    ep = torch.zeros(512, dtype=torch.int32, device="cuda")
+    ep = torch.zeros(lib.svtad_allreduce_epoch_bytes() // 4, dtype=torch.int32, device="cuda")
     assert lib.svtad_allreduce_sum(ptrs, 0, 2, 100, _lib.BF16, 4096, ep.data_ptr(), 0, None) == _lib.ERR_ARG      # not a multiple of 16
     assert lib.svtad_allreduce_sum(ptrs, 2, 2, 1024, _lib.BF16, 4096, ep.data_ptr(), 0, None) == _lib.ERR_ARG     # rank out of range
     assert lib.svtad_allreduce_sum(ptrs, 0, 2, 1024, _lib.F32, 4096, ep.data_ptr(), 0, None) == _lib.ERR_ARG      # 16-bit only
-    assert lib.svtad_allreduce_sum(ptrs, 0, 2, 1024, _lib.BF16, 1024, ep.data_ptr(), 0, None) == _lib.ERR_ARG     # flags inside the bucket
+    assert lib.svtad_allreduce_sum(ptrs, 0, 2, 1024, _lib.BF16, 1024, ep.data_ptr(), 0, None) == _lib.ERR_ARG     # staging inside the bucket
     assert lib.svtad_allreduce_sum(ptrs, 0, 1, 1024, _lib.BF16, 4096, ep.data_ptr(), 0, None) == 0                # one rank: nothing to do

@@ -85,16 +85,13 @@ def test_two_gloo_ranks_match_single_rank():
 
 
 def test_two_shot_slices_partition_the_bucket():
-    """The slices / CTA shares of the peer-memory exchange cover the bucket exactly once, in whole 16-byte vectors."""
-    for numel, world, ctas in [(995904, 8, 32), (995904, 2, 32), (1024, 4, 1), (64 * 3, 3, 5), (padded_numel(1000, 8), 8, 7)]:
+    """The slices of the peer-memory exchange cover the bucket exactly once, in whole 16-byte units."""
+    for numel, world in [(995904, 8), (995904, 2), (1024, 4), (64 * 3, 3), (padded_numel(1000, 8), 8)]:
         seen = np.zeros(numel, dtype=np.int32)
         for r in range(world):
-            (lo, hi), shares = slice_bounds(numel, r, world, ctas)
+            lo, hi = slice_bounds(numel, r, world)
             assert lo % 8 == 0 and hi % 8 == 0 and hi - lo == numel // world
-            assert shares[0][0] == lo and max(b for _, b in shares) == hi
-            for a, b in shares:
-                assert a % 8 == 0 and b % 8 == 0 and lo <= a <= b <= hi
-                seen[a:b] += 1
+            seen[lo:hi] += 1
         assert (seen == 1).all()
     assert padded_numel(995904, 8) % (64 * 8) == 0 and padded_numel(995904, 8) - 995904 < 64 * 8
     import pytest
