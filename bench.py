@@ -232,8 +232,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying CUDA graphs")
-    ap.add_argument("--layer-streams", type=int, default=0, choices=[0, 1],
-                    help="1: the step's three layers (keep rates) run on three streams instead of one after the other")
+    ap.add_argument("--layer-streams", type=int, default=1, choices=[0, 1],
+                    help="1 (default): the step's three layers (keep rates), which do not depend on one another, run on "
+                         "three streams; 0: one after the other")
+    ap.add_argument("--ar-per-layer", type=int, default=0, choices=[0, 1],
+                    help="N > 1: 1 = one gradient bucket per layer, exchanged while the other layers still compute")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-ref-cuda", action="store_true")
     ap.add_argument("--workload", default="sparseconv", choices=["sparseconv", "backbone"],
@@ -291,21 +294,31 @@ def main():
     y_buf = torch.empty(n_max, C, dtype=torch.bfloat16, device=dev)
     gx_buf = torch.empty(n_max, C, dtype=torch.bfloat16, device=dev)
     LAUNCHES_PER_LAYER = 4   # fwd, dgrad, wgrad partials (bias row included), reduce
-    # one flat bucket for the gradients of the step's three layers (gw ++ gb each), all-reduced once per step
-    # the way DDP buckets the adapters' gradients (reference: src/eccv26_tad.py:288-300, 25 MB buckets)
+    # Gradient buckets (gw ++ gb per layer).  N > 1: they live in peer-mapped memory and are summed by
+    # svtad_allreduce_sum (two-shot exchange by plain stores over NVLink that carry their own flags, bounded waits,
+    # small CTAs that fit beside the compute kernels' CTAs); SVTAD_BENCH_ALLREDUCE=nccl keeps ordinary tensors +
+    # NCCL.  The ranks decide together (one collective vote) before any set-up call; a "no" puts all of them on
+    # NCCL.  --ar-per-layer 1: one bucket per layer, exchanged as soon as that layer's weight gradient is done, the
+    # way DDP overlaps its bucket all-reduces with the rest of the backward (reference: src/eccv26_tad.py:288-300);
+    # 0: one bucket for the step, exchanged at its end.  All exchanges go to ONE stream in layer order, so every
+    # rank issues them in the same order.
     per_layer = KK * C * C + C
-    n_grads = len(KEEPS) * per_layer
-    # N > 1: the bucket lives in peer-mapped memory and is summed by svtad_allreduce_sum (two-shot exchange by plain
-    # loads and stores over NVLink, bounded waits); SVTAD_BENCH_ALLREDUCE=nccl keeps an ordinary tensor + NCCL.
-    # The ranks decide together (one collective vote) before any set-up call; a "no" puts all of them on NCCL.
     from eccv26_tad_b200.distributed import GradBucket
-    bucket = GradBucket(n_grads, torch.bfloat16, dev,
-                        exchange="collective" if os.environ.get("SVTAD_BENCH_ALLREDUCE", "peer") == "nccl" else "peer")
-    grads, allreduce_kind = bucket.buffer, bucket.kind
-    if world > 1 and bucket.kind == "nccl" and hasattr(bucket, "fallback_reason"):
-        sys.stderr.write(f"[bench] peer-memory all-reduce unavailable ({bucket.fallback_reason}); using NCCL\n")
-    gw_bufs = [grads[i * per_layer:i * per_layer + KK * C * C] for i in range(len(KEEPS))]
-    gb_bufs = [grads[i * per_layer + KK * C * C:(i + 1) * per_layer] for i in range(len(KEEPS))]
+    want_peer = os.environ.get("SVTAD_BENCH_ALLREDUCE", "peer") != "nccl"
+    exch = "peer" if want_peer else "collective"
+    if args.ar_per_layer:
+        buckets = [GradBucket(per_layer, torch.bfloat16, dev, exchange=exch) for _ in KEEPS]
+        gw_bufs = [b.buffer[:KK * C * C] for b in buckets]
+        gb_bufs = [b.buffer[KK * C * C:per_layer] for b in buckets]
+    else:
+        buckets = [GradBucket(len(KEEPS) * per_layer, torch.bfloat16, dev, exchange=exch)]
+        grads = buckets[0].buffer
+        gw_bufs = [grads[i * per_layer:i * per_layer + KK * C * C] for i in range(len(KEEPS))]
+        gb_bufs = [grads[i * per_layer + KK * C * C:(i + 1) * per_layer] for i in range(len(KEEPS))]
+    allreduce_kind = buckets[0].kind
+    if world > 1 and want_peer and buckets[0].kind == "nccl":
+        sys.stderr.write(f"[bench] peer-memory all-reduce unavailable ({getattr(buckets[0], 'fallback_reason', '?')}); using NCCL\n")
+    comm = torch.cuda.Stream(device=dev)
     gw_buf, gb_buf = gw_bufs[0], gb_bufs[0]
     launches_per_step = 0
 
@@ -318,10 +331,28 @@ def main():
     lanes = [torch.cuda.Stream(device=dev) for _ in KEEPS]
 
     def raw_step(dk, stream=None, count=False):
-        """One step through the C ABI on resident buffers: 3 keep rates x (fwd, then dgrad and wgrad+bias).
-        The two halves of the backward are independent, so wgrad runs on a side stream next to dgrad."""
+        """One step through the C ABI on resident buffers: 3 keep rates x (fwd, dgrad, wgrad+bias).  The passes of a
+        layer are independent of one another here (the upstream gradient is an input), so the weight gradient runs
+        on a side stream next to forward and input gradient.  With N > 1 the weight gradients are issued first and
+        the all-reduce of their bucket follows them on a stream of its own, so that - as under DDP - the exchange
+        runs while the rest of the step still computes."""
         nl = 0
         cur = torch.cuda.current_stream()
+        early_wgrad = world > 1 and not args.ar_per_layer and args.layer_streams
+
+        def wgrad(li, it, st):
+            ops._lib.check(lib.svtad_conv_wgrad(it["gy"].data_ptr(), it["x"].data_ptr(), it["table"].data_ptr(),
+                                                gw_bufs[li].data_ptr(), gb_bufs[li].data_ptr(), it["n"], C, C, KK, 0, code,
+                                                ws_l[li].data_ptr(), ws_bytes, st.cuda_stream))
+
+        if early_wgrad:
+            for li, it in enumerate(dk):
+                sides[li].wait_stream(cur)
+                wgrad(li, it, sides[li])
+                comm.wait_stream(sides[li])
+            with torch.cuda.stream(comm):
+                buckets[0].all_reduce()
+            nl += 1
         for li, it in enumerate(dk):
             n = it["n"]
             main = lanes[li] if args.layer_streams else cur
@@ -331,20 +362,29 @@ def main():
             ops._lib.check(lib.svtad_conv_fwd(it["x"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(),
                                               bias.data_ptr(), y_bufs[li].data_ptr(), n, C, C, KK, 0, code, None, 0,
                                               main.cuda_stream))
-            side.wait_stream(main)
-            ops._lib.check(lib.svtad_conv_wgrad(it["gy"].data_ptr(), it["x"].data_ptr(), it["table"].data_ptr(),
-                                                gw_bufs[li].data_ptr(), gb_bufs[li].data_ptr(), n, C, C, KK, 0, code,
-                                                ws_l[li].data_ptr(), ws_bytes, side.cuda_stream))
+            if not early_wgrad:
+                side.wait_stream(main)
+                wgrad(li, it, side)
             ops._lib.check(lib.svtad_conv_dgrad(it["gy"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(),
                                                 gx_bufs[li].data_ptr(), n, C, C, KK, 0, code, None, None, 0,
                                                 main.cuda_stream))
-            main.wait_stream(side)
+            if world > 1 and args.ar_per_layer:
+                comm.wait_stream(side)
+                with torch.cuda.stream(comm):
+                    buckets[li].all_reduce()
+                nl += 1
+            if not early_wgrad:
+                main.wait_stream(side)
             nl += LAUNCHES_PER_LAYER
         if args.layer_streams:
             for li in range(len(dk)):
                 cur.wait_stream(lanes[li])
         if world > 1:
-            bucket.all_reduce()
+            if args.ar_per_layer or early_wgrad:
+                cur.wait_stream(comm)
+            else:
+                buckets[0].all_reduce()
+                nl += 1
         return nl
 
     stream = torch.cuda.Stream(device=dev)
