@@ -14,7 +14,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 OBJ = os.path.join(PKG, "_build")
 LIB = os.path.join(PKG, "libsvtad.so")
-SOURCES = ["api.cu", "table.cu", "conv_simt.cu", "conv_tc.cu", "conv_tc_hybrid.cu", "conv_tc_pair.cu", "allreduce.cu", "noalloc.cu"]
+SOURCES = ["api.cu", "table.cu", "conv_simt.cu", "conv_simt_fwd.cu", "conv_tc.cu", "conv_tc_hybrid.cu", "conv_tc_pair.cu", "allreduce.cu", "noalloc.cu"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

@@ -47,6 +47,9 @@ struct ConvArgs {
 
 // CUDA-core kernels (conv_simt.cu)
 int simt_fwd(const ConvArgs& p, cudaStream_t s);
+// fp32 forward tuned for the FFMA rate (conv_simt_fwd.cu)
+bool simt_fwd_f32_supported(const ConvArgs& p);
+int simt_fwd_f32(const ConvArgs& p, cudaStream_t s);
 int simt_dgrad_gather(const ConvArgs& p, const int32_t* status, cudaStream_t s);
 int simt_dgrad_scatter(const ConvArgs& p, const int32_t* status, float* ws, cudaStream_t s);
 int simt_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw, void* gb, int64_t n,

@@ -8,6 +8,8 @@
 //   MODE_DGATHER  gx[j,:]   = sum_k' gy[nbr[j,k']] . W[KK-1-k']^T          (A = gy, B = W^T; symmetric tables)
 //   MODE_DSCATTER gx[nbr[i,k],:] += gy[i] . W[k]^T  (fp32 atomics into a workspace; any table,
 //                 the reference's own formulation, 2d_sparse_v3.cu:679-707)
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace svtad {
@@ -238,7 +240,10 @@ static int dispatch_conv_simt(const ConvArgs& p, const int32_t* status, float* w
     return set_error(SVTAD_ERR_UNSUPPORTED, "unknown dtype %d", p.dtype);
 }
 
-int simt_fwd(const ConvArgs& p, cudaStream_t s) { return dispatch_conv_simt<MODE_FWD>(p, nullptr, nullptr, s); }
+int simt_fwd(const ConvArgs& p, cudaStream_t s) {
+    if (simt_fwd_f32_supported(p) && getenv("SVTAD_SIMT_FWD_GENERIC") == nullptr) return simt_fwd_f32(p, s);
+    return dispatch_conv_simt<MODE_FWD>(p, nullptr, nullptr, s);
+}
 
 int simt_dgrad_gather(const ConvArgs& p, const int32_t* status, cudaStream_t s) {
     return dispatch_conv_simt<MODE_DGATHER>(p, status, nullptr, s);

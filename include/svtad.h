@@ -221,6 +221,14 @@ int svtad_allreduce_sum_emulated(void* const* bufs, int world, int64_t n_elems, 
 int svtad_device_error(int32_t* code_out);
 
 /*
+ * Measurement aid: launches one kernel of `ctas` x 256 threads that does nothing but iters * 64 dependent-chain
+ * FMAs per thread (8 independent chains), i.e. 2 * 64 * iters * ctas * 256 flops.  Timed by the caller with events
+ * on `stream`, it gives the FFMA rate the CUDA-core (fp32) kernels are measured against.  `scratch` is one float
+ * of device memory (never written).  No reference counterpart.
+ */
+int svtad_ffma_probe(int ctas, int iters, float* scratch, void* stream);
+
+/*
  * Which implementation the given problem dispatches to: 0 = CUDA-core (SIMT) kernels,
  * 1 = tcgen05 tensor-core kernels.  Honours the SVTAD_FORCE_PATH=simt|tc environment override.
  */
