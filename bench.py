@@ -239,8 +239,10 @@ def main():
                     help="N > 1: 1 = one gradient bucket per layer, exchanged while the other layers still compute")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--skip-ref-cuda", action="store_true")
-    ap.add_argument("--workload", default="sparseconv", choices=["sparseconv", "backbone"],
-                    help="backbone: forward of the ViT-B sparse-adapter backbone on 160-frame clips (secondary line)")
+    ap.add_argument("--workload", default="sparseconv", choices=["sparseconv", "backbone", "configs"],
+                    help="backbone: forward of the ViT-B sparse-adapter backbone on 160-frame clips (secondary line); "
+                         "configs: the other benchmark configurations (--configs 1,3,4), one JSON line each")
+    ap.add_argument("--configs", default="1,3,4")
     ap.add_argument("--backbone-train", action="store_true",
                     help="with --workload backbone: one training step (forward, backward to the adapters, AdamW) per step")
     ap.add_argument("--kernel-case", default=None, choices=["fwd", "dgrad", "wgrad", "table"],
@@ -254,6 +256,8 @@ def main():
         return kernel_case(args)
     if args.workload == "backbone":
         return backbone_case(args)
+    if args.workload == "configs":
+        return configs_case(args)
     if args.impl == "reference":
         return reference_arm(args)
 
@@ -496,10 +500,14 @@ def main():
                                       "wgrad": "wgrad_hybrid_kernel<BN> + wgrad_reduce4_kernel"}[dominant],
         "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
         "peak_source": f"{peak_kind} bf16 burst", "traffic": NCU_DRAM_BYTES_PER_ROW[dominant] * tokens_step / len(KEEPS),
-        "traffic_note": "ncu DRAM bytes per row of the 226560-row capture x mean rows per launch",
+        "traffic_note": "not measured in this run: a constant, the ncu DRAM bytes per row of the captures summarised under "
+                        "profiles/ times the mean rows per launch",
         "flops_per_launch": {f"keep{int(r * 100)}": flops_pass(host_sets[0][ki]["n"]) for ki, r in enumerate(KEEPS)},
         "ms_per_launch": {f"{name}_keep{int(KEEPS[ki] * 100)}": v for (name, ki), v in per_kernel.items()},
         "all_kernels_frac": {name: dom_flops / (totals[name] * 1e-3) / 1e12 / peak_tf for name in totals},
+        "frac_per_launch": {f"{name}_keep{int(KEEPS[ki] * 100)}": flops_pass(host_sets[0][ki]["n"]) / (v * 1e-3) / 1e12 / peak_tf
+                            for (name, ki), v in per_kernel.items()},
+        "whole_step_frac": 3 * dom_flops / (ms_total / args.steps * 1e-3) / 1e12 / peak_tf,
     }
 
     # ---------------------------------------------------------------- e2e through the public API, host buffers
@@ -641,7 +649,7 @@ def main():
     ref_cuda = None
     if rank == 0 and not args.skip_ref_cuda:
         try:
-            ref_cuda = time_reference_cuda(dsets, weight, bias, stream)
+            ref_cuda = time_reference_cuda(dsets, weight, bias, stream, roofline["ms_per_launch"])
         except Exception as e:
             ref_cuda = {"unavailable": str(e)[:200]}
 
@@ -802,36 +810,219 @@ def kernel_case(args):
                       "flops": flops_pass(n), "TFLOP/s_best": flops_pass(n) / (min(ms) * 1e-3) / 1e12}))
 
 
-def time_reference_cuda(dsets, weight, bias, stream):
-    """The reference's own CUDA extension (prebuilt under oracle/_ref/) on the same resident inputs."""
+def _time_eager(fn, reps, warm=3):
+    """Average milliseconds of `reps` eager calls of fn(i) on the legacy default stream (where the reference's
+    extension launches), after `warm` untimed ones."""
+    import torch
+    for i in range(warm):
+        fn(i)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(reps):
+        fn(warm + i)
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+def time_reference_cuda(dsets, weight, bias, stream, ours_ms_per_launch=None):
+    """The reference's own CUDA extension (prebuilt under oracle/_ref/) on the same resident inputs, per keep rate:
+    its own dispatch for C_in >= 128 (implicit_gemm_fwd_v2_chunked, then bwd_in, bwd_w and the bias sum), 50 eager
+    repetitions per keep rate on rotating input sets."""
     import torch
     from oracle import build_ref
     mod = build_ref.load_built()
     if mod is None:
         return {"unavailable": "oracle/_ref extension not built"}
-    reps = 5
-    tokens = sum(it["n"] for it in dsets[0])
-
-    def step(dk):
-        for it in dk:
-            n = it["n"]
+    reps = 50
+    per_keep = {}
+    total_ms = 0.0
+    for ki, r in enumerate(KEEPS):
+        def layer(i, ki=ki):
+            it = dsets[i % N_SETS][ki]
             mod.implicit_gemm_fwd_v2_chunked(it["x"], it["table"], weight, bias, 0, 4096)
-            mod.bwd_in(it["gy"], it["table"], weight, n, C, 0)
+            mod.bwd_in(it["gy"], it["table"], weight, it["n"], C, 0)
             mod.bwd_w(it["gy"], it["x"], it["table"], C, 0)
             it["gy"].sum(0)
-    # the reference launches on the legacy default stream: time on it
-    torch.cuda.synchronize()
-    step(dsets[0])
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for i in range(reps):
-        step(dsets[(i + 1) % N_SETS])
-    b.record()
-    torch.cuda.synchronize()
-    ms = a.elapsed_time(b) / reps
-    return {"value": tokens / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms, "steps": reps,
-            "what": "reference extension (implicit_gemm_fwd_v2_chunked + bwd_in + bwd_w + sum) recompiled for sm_100a, eager launches"}
+        ms = _time_eager(layer, reps)
+        n = dsets[0][ki]["n"]
+        row = {"ms": ms, "tokens_per_s": n / (ms * 1e-3), "TFLOP/s": 3 * flops_pass(n) / (ms * 1e-3) / 1e12}
+        if ours_ms_per_launch is not None:
+            ours = sum(ours_ms_per_launch[f"{name}_keep{int(r * 100)}"] for name in ("fwd", "dgrad", "wgrad"))
+            row["ours_ms"] = ours
+            row["speedup"] = ms / ours
+        per_keep[f"keep{int(r * 100)}"] = row
+        total_ms += ms
+    tokens = sum(it["n"] for it in dsets[0])
+    return {"value": tokens / (total_ms * 1e-3), "unit": "tokens/s", "ms_per_step": total_ms, "steps": reps,
+            "per_keep": per_keep,
+            "what": "reference extension (implicit_gemm_fwd_v2_chunked + bwd_in + bwd_w + sum) recompiled for sm_100a; "
+                    "eager launches, 50 repetitions per keep rate; ours_ms = the three kernels of this library for the "
+                    "same layer, timed back to back from a CUDA graph"}
+
+
+# ------------------------------------------------------------------------------------------ other configurations
+def _graph_time(fn, reps=24):
+    """Average microseconds of one fn(i, stream) launch: `reps` launches captured into one CUDA graph and replayed."""
+    import torch
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        fn(0, st.cuda_stream)
+        st.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            for i in range(reps):
+                fn(i, torch.cuda.current_stream().cuda_stream)
+        g.replay()
+        st.synchronize()
+        best = None
+        for _ in range(3):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(st)
+            g.replay()
+            b.record(st)
+            b.synchronize()
+            t = a.elapsed_time(b) / reps
+            best = t if best is None else min(best, t)
+    return best * 1e3
+
+
+def ffma_peak_tflops():
+    """FFMA rate of this GPU (what the fp32 CUDA-core kernels are measured against): svtad_ffma_probe timed here."""
+    import torch
+    from eccv26_tad_b200 import _lib
+    lib = _lib.load()
+    scratch = torch.zeros(4, device="cuda")
+    ctas, iters = 148 * 8, 4000
+    us = _graph_time(lambda i, sc: _lib.check(lib.svtad_ffma_probe(ctas, iters, scratch.data_ptr(), sc)), 5)
+    return 2.0 * 64 * iters * ctas * 256 / (us * 1e-6) / 1e12
+
+
+def configs_case(args):
+    """Secondary lines, one JSON line each: the benchmark configurations other than the headline one, every kernel
+    with its fraction of the roofline that bounds it and the reference's CUDA path beside it where that can run.
+      config1  fp32 forward, batch 1 x T=8, C=192, keep 50 % (784 rows)            -> fraction of the FFMA rate
+      config3  bf16 fwd / dgrad / wgrad, batch 4 x T=80, keep 30 % (18 880 rows), C in {256, 768, 1024}, 3x3 and 5x5
+      config4  neighbor-table construction alone, 3072 slices, keep {10, 25, 50} %  -> fraction of HBM bandwidth"""
+    import torch
+    from eccv26_tad_b200 import _lib, build_neighbor_table, ops
+    from eccv26_tad_b200.backbone import _torch_remap
+    from oracle import build_ref
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    lib = _lib.load()
+    ref = build_ref.load_built()
+    peak_tf, peak_hbm, peak_kind = measured_peaks()
+    want = args.configs.split(",")
+
+    def table_for(slices, keep, ks, seed):
+        g = torch.Generator().manual_seed(seed)
+        scores = torch.randn(slices, H * W, generator=g).to(dev)
+        return scores, build_neighbor_table(scores, num_keep=num_keep(keep, H * W), h=H, w=W, kernel_size=ks)
+
+    if "1" in want:
+        ffma = ffma_peak_tflops()
+        _, (kept, table) = table_for(8, 0.5, 3, 1235)
+        n = table.shape[0]
+        g = torch.Generator().manual_seed(1235)
+        x = torch.randn(n, C, generator=g).to(dev)
+        w = (torch.randn(C, C, 3, 3, generator=g) * math.sqrt(2.0 / (C * 9))).view(C, C, 9).permute(2, 1, 0).contiguous().to(dev)
+        b = torch.zeros(C, device=dev)
+        y = torch.empty(n, C, device=dev)
+        us = _graph_time(lambda i, sc: _lib.check(lib.svtad_conv_fwd(x.data_ptr(), table.data_ptr(), w.data_ptr(), b.data_ptr(),
+                                                                     y.data_ptr(), n, C, C, 9, 0, _lib.F32, None, 0, sc)))
+        fl = 2.0 * n * 9 * C * C
+        line = {"metric": "SparseConv2D forward fp32 (config 1), retained tokens/s", "value": n / (us * 1e-6), "unit": "tokens/s",
+                "config": {"workload": "fp32 forward, batch 1 x T=8 x 14x14, Cin=Cout=192, 3x3, keep 50 % (784 rows)"},
+                "us_per_launch": us, "dtype": "f32", "data": "synthetic",
+                "roofline": {"bound": "ffma", "achieved": fl / (us * 1e-6) / 1e12, "peak": ffma, "unit": "TFLOP/s",
+                             "frac": fl / (us * 1e-6) / 1e12 / ffma, "peak_source": "svtad_ffma_probe timed in this run",
+                             "flops": "dense-equivalent 2*N*KK*Cin*Cout"}}
+        if ref is not None:
+            ms = _time_eager(lambda i: ref.implicit_gemm_fwd_v2(x, table, w, b, 0), 50)
+            line["reference_cuda"] = {"us_per_launch": ms * 1e3, "speedup": ms * 1e3 / us,
+                                      "what": "implicit_gemm_fwd_v2 in fp32 (gather + cuBLAS SGEMM, TF32 off + reduce), eager"}
+        print(json.dumps(line), flush=True)
+
+    if "3" in want:
+        for Cc in (256, 768, 1024):
+            for ks in (3, 5):
+                kk = ks * ks
+                _, (kept, table) = table_for(4 * 80, 0.3, ks, 1237)
+                n = table.shape[0]
+                x = torch.randn(n, Cc, device=dev).bfloat16()
+                gy = torch.randn(n, Cc, device=dev).bfloat16()
+                w = (torch.randn(kk, Cc, Cc, device=dev) * math.sqrt(2.0 / (Cc * kk))).bfloat16()
+                b = torch.zeros(Cc, device=dev).bfloat16()
+                y = torch.empty(n, Cc, dtype=torch.bfloat16, device=dev)
+                gw = torch.empty(kk, Cc, Cc, dtype=torch.bfloat16, device=dev)
+                gb = torch.empty(Cc, dtype=torch.bfloat16, device=dev)
+                ws_bytes = lib.svtad_workspace_bytes(_lib.OP_WGRAD, n, Cc, Cc, kk, _lib.BF16)
+                ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+                code = _lib.BF16
+                t = {
+                    "fwd": _graph_time(lambda i, sc: _lib.check(lib.svtad_conv_fwd(x.data_ptr(), table.data_ptr(), w.data_ptr(), b.data_ptr(), y.data_ptr(), n, Cc, Cc, kk, 0, code, None, 0, sc)), 6),
+                    "dgrad": _graph_time(lambda i, sc: _lib.check(lib.svtad_conv_dgrad(gy.data_ptr(), table.data_ptr(), w.data_ptr(), y.data_ptr(), n, Cc, Cc, kk, 0, code, None, None, 0, sc)), 6),
+                    "wgrad": _graph_time(lambda i, sc: _lib.check(lib.svtad_conv_wgrad(gy.data_ptr(), x.data_ptr(), table.data_ptr(), gw.data_ptr(), gb.data_ptr(), n, Cc, Cc, kk, 0, code, ws.data_ptr(), ws_bytes, sc)), 6),
+                }
+                fl = 2.0 * n * kk * Cc * Cc
+                total_us = sum(t.values())
+                line = {"metric": "SparseConv2D fwd+bwd bf16 (config 3), retained tokens/s", "value": n / (total_us * 1e-6),
+                        "unit": "tokens/s", "dtype": "bf16", "data": "synthetic",
+                        "config": {"workload": f"bf16 fwd+dgrad+wgrad, batch 4 x T=80 x 14x14, keep 30 % ({n} rows), Cin=Cout={Cc}, {ks}x{ks}"},
+                        "us_per_launch": t,
+                        "roofline": {"bound": "tensor", "peak": peak_tf, "unit": "TFLOP/s", "peak_source": f"{peak_kind} bf16 burst",
+                                     "achieved": {k: fl / (v * 1e-6) / 1e12 for k, v in t.items()},
+                                     "frac": {k: fl / (v * 1e-6) / 1e12 / peak_tf for k, v in t.items()},
+                                     "frac_fwd_bwd": 3 * fl / (total_us * 1e-6) / 1e12 / peak_tf}}
+                if ref is None:
+                    pass
+                elif ks != 3:
+                    line["reference_cuda"] = "unsupported kernel size (the reference's kernels are 3x3 only)"
+                else:
+                    def layer(i):
+                        ref.implicit_gemm_fwd_v2_chunked(x, table, w, b, 0, 4096)
+                        ref.bwd_in(gy, table, w, n, Cc, 0)
+                        ref.bwd_w(gy, x, table, Cc, 0)
+                        gy.sum(0)
+                    ms = _time_eager(layer, 5 if Cc > 256 else 20, warm=1)
+                    line["reference_cuda"] = {"us_fwd_bwd": ms * 1e3, "speedup": ms * 1e3 / total_us, "what": "eager"}
+                print(json.dumps(line), flush=True)
+                del x, gy, w, y, gw, ws
+
+    if "4" in want:
+        slices = 8 * 384
+        full = ops.table_init(slices, 1, H, W, 3, dev)            # one 14x14 slice per row of the batch dimension
+        for keep in (0.10, 0.25, 0.50):
+            k = num_keep(keep, H * W)
+            g = torch.Generator().manual_seed(1238)
+            scores = torch.randn(slices, H * W, generator=g).to(dev)
+            kept = torch.empty(slices, k, dtype=torch.int32, device=dev)
+            table = torch.empty(slices * k, 9, dtype=torch.int32, device=dev)
+            us = _graph_time(lambda i, sc: _lib.check(lib.svtad_table_build(scores.data_ptr(), slices, H * W, k, H, W, 3,
+                                                                            kept.data_ptr(), table.data_ptr(), sc)), 10)
+
+            def torch_ops(i):
+                idx = torch.topk(scores, k, dim=1, largest=True)[1].sort(dim=1)[0]
+                return idx, _torch_remap(full, idx)
+            ms = _time_eager(torch_ops, 20)
+            idx, tref = torch_ops(0)
+            same = bool(torch.equal(tref.reshape(-1, 9), table) and torch.equal(idx.to(torch.int32), kept))
+            n = slices * k
+            bytes_ = 4 * slices * H * W + 4 * n + 4 * n * 9
+            line = {"metric": "neighbor-table construction (config 4), retained tokens/s", "value": n / (us * 1e-6),
+                    "unit": "tokens/s", "dtype": "int32", "data": "synthetic",
+                    "config": {"workload": f"top-k + 3x3 table, {slices} slices of 14x14 fp32 scores, keep {int(keep * 100)} % ({n} rows)"},
+                    "us_per_launch": us,
+                    "roofline": {"bound": "hbm", "achieved": bytes_ / (us * 1e-6) / 1e9, "peak": peak_hbm, "unit": "GB/s",
+                                 "frac": bytes_ / (us * 1e-6) / 1e9 / peak_hbm, "peak_source": f"{peak_kind} copy bandwidth",
+                                 "bytes": "4*S*L scores + 4*N kept + 36*N table"},
+                    "torch_ops": {"us": ms * 1e3, "speedup": ms * 1e3 / us, "bit_identical": same,
+                                  "what": "topk + sort + gather + remap of the reference restated in torch ops on the same GPU "
+                                          "(vit_sparse_adapter_poguise.py:785-787, 913-977), full-grid table precomputed, eager"}}
+            print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":

@@ -9,44 +9,51 @@
 //     -1 rows zero-filled without touching memory), weight rows as [channel][column],
 //   * strict fp32 FMA accumulation in (tap, channel) ascending order inside a tap group,
 //   * taps that no row of the tile uses are skipped,
-//   * small problems: the taps are split over the G CTAs of a thread-block cluster, which sum their tiles through
+//   * small problems: the K steps are split over the G CTAs of a thread-block cluster, which sum their tiles through
 //     distributed shared memory in a fixed order (deterministic, no atomics) - so that a 784-row call still
-//     spreads over the whole GPU.
+//     spreads over the whole GPU.  The (tap, channel block) steps are dealt out evenly, whatever the tap count.
 #include <cstdlib>
 
 #include "common.cuh"
 
 namespace svtad {
 
-constexpr int F_BM = 64, F_BN = 64, F_BK = 32, F_THREADS = 128, F_STAGES = 3;
+constexpr int F_BK = 32, F_STAGES = 3;
 constexpr int F_ASTR = F_BK + 4;          // floats per gathered row in shared memory (144 B: 16-byte aligned, conflict-free)
 constexpr int F_MAX_KK = 49;
-constexpr int F_RSTR = F_BN + 4;          // row stride of the tile parked for the cluster reduction
 
 __device__ __forceinline__ void f_cp16(uint32_t dst, const void* src, uint32_t bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
 
+template <int F_BM, int F_BN>
 struct FwdSmem {
     float a[F_STAGES][F_BM * F_ASTR];
     float b[F_STAGES][F_BK * F_BN];
     int nbr[F_BM * F_MAX_KK];
     int any[F_MAX_KK];
+    int n_act;
 };
 
-template <int G>
-__global__ void __launch_bounds__(F_THREADS)
+// G = CTAs of a cluster that share a tile's taps; the tile is F_BM x F_BN, every thread owns RPT rows x 4 columns of
+// it (F_THREADS = F_BM * F_BN / (4 * RPT)): 8 rows for large calls (fewest shared-memory loads per FMA), 4 rows for
+// small ones (twice the warps to hide latency with).
+template <int G, int F_BM, int F_BN, int RPT>
+__global__ void __launch_bounds__(F_BM * F_BN / (4 * RPT))
 conv_fwd_f32_kernel(const float* __restrict__ x, const int32_t* __restrict__ nbr, const float* __restrict__ w,
                     const float* __restrict__ bias, float* __restrict__ out, long n, int cin, int cout, int kk,
                     int tpb, int tiles_n) {
+    constexpr int F_THREADS = F_BM * F_BN / (4 * RPT);
+    constexpr int TXN = F_BN / 4;                      // threads along the columns
+    constexpr int TYN = F_THREADS / TXN;               // threads along the rows: thread ty owns rows ty + TYN * i
+    constexpr int F_RSTR = F_BN + 4;                   // row stride of the tile parked for the cluster reduction
     extern __shared__ __align__(16) unsigned char f_smem_raw[];
-    FwdSmem& sm = *reinterpret_cast<FwdSmem*>(f_smem_raw);
+    FwdSmem<F_BM, F_BN>& sm = *reinterpret_cast<FwdSmem<F_BM, F_BN>*>(f_smem_raw);
     const int tid = threadIdx.x;
-    const int tx = tid & 15, ty = tid >> 4;            // columns tx * 4 .. + 3, rows ty + 8 * i
+    const int tx = tid % TXN, ty = tid / TXN;          // columns tx * 4 .. + 3, rows ty + TYN * i
     const int tile = blockIdx.x / G, grp = blockIdx.x % G;
     const long row0 = (long)(tile / tiles_n) * F_BM;
     const int n0 = (tile % tiles_n) * F_BN;
-    const int k_lo = grp * kk / G, k_hi = (grp + 1) * kk / G;
 
     for (int t = tid; t < kk; t += F_THREADS) sm.any[t] = 0;
     __syncthreads();
@@ -54,7 +61,7 @@ conv_fwd_f32_kernel(const float* __restrict__ x, const int32_t* __restrict__ nbr
         const int r = e / kk, k = e - r * kk;
         const long i = row0 + r;
         int v = -1;
-        if (i < n && k >= k_lo && k < k_hi) {
+        if (i < n) {
             const int j = __ldg(nbr + i * kk + k);
             if (j != -1) {
                 const long jj = (long)j + (tpb > 0 ? (i / tpb) * (long)tpb : 0);
@@ -66,19 +73,25 @@ conv_fwd_f32_kernel(const float* __restrict__ x, const int32_t* __restrict__ nbr
     }
     __syncthreads();
 
-    // the K steps of this CTA: (tap, 32-channel block) for every tap of the group that some row uses
+    // The K steps of the tile are (tap, 32-channel block) for every tap that some row uses, taps ascending; the G
+    // CTAs of the cluster take equal contiguous shares of them (a share may start in the middle of a tap).
     const int cblk = (cin + F_BK - 1) / F_BK;
-    int n_taps = 0;
-    for (int k = k_lo; k < k_hi; ++k) n_taps += sm.any[k];
-    const int steps = n_taps * cblk;
-    // step -> (tap, c0): walked incrementally by the loader
-    int ld_k = k_lo, ld_c = 0;
-    auto advance_tap = [&](int& k) { while (k < k_hi && !sm.any[k]) ++k; };
-    advance_tap(ld_k);
+    if (tid == 0) {
+        int m = 0;
+        for (int k = 0; k < kk; ++k)
+            if (sm.any[k]) sm.any[m++] = k;           // compacted in place: any[0 .. m) = the taps in use (m <= k always)
+        sm.n_act = m;
+    }
+    __syncthreads();
+    const int total_steps = sm.n_act * cblk;
+    const int st_lo = (int)((long)grp * total_steps / G), st_hi = (int)((long)(grp + 1) * total_steps / G);
+    const int steps = st_hi - st_lo;
+    int ld_t = st_lo / cblk, ld_c = (st_lo % cblk) * F_BK;     // position of the loader: index into any[], channel
     auto load_stage = [&](int stage) {
-        // A: 64 rows x F_BK / 4 chunks of 16 B; B: F_BK channel rows x 16 chunks of 16 B
+        // A: F_BM rows x F_BK / 4 chunks of 16 B; B: F_BK channel rows x F_BN / 4 chunks of 16 B
         const uint32_t a_base = (uint32_t)__cvta_generic_to_shared(sm.a[stage]);
         const uint32_t b_base = (uint32_t)__cvta_generic_to_shared(sm.b[stage]);
+        const int ld_k = sm.any[ld_t];
 #pragma unroll
         for (int q = 0; q < (F_BM * F_BK / 4) / F_THREADS; ++q) {
             const int g = tid + q * F_THREADS;
@@ -91,18 +104,18 @@ conv_fwd_f32_kernel(const float* __restrict__ x, const int32_t* __restrict__ nbr
 #pragma unroll
         for (int q = 0; q < (F_BK * F_BN / 4) / F_THREADS; ++q) {
             const int g = tid + q * F_THREADS;
-            const int cr = g >> 4, ch = g & 15;
+            const int cr = g / TXN, ch = g % TXN;
             const int c = ld_c + cr, nn = n0 + ch * 4;
             const bool ok = c < cin && nn < cout;
             f_cp16(b_base + (cr * F_BN + ch * 4) * 4, ok ? w + ((long)ld_k * cin + c) * cout + nn : w, ok ? 16u : 0u);
         }
         ld_c += F_BK;
-        if (ld_c >= cin) { ld_c = 0; ++ld_k; advance_tap(ld_k); }
+        if (ld_c >= cin) { ld_c = 0; ++ld_t; }
     };
 
-    float acc[8][4];
+    float acc[RPT][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < RPT; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
 
@@ -114,21 +127,21 @@ conv_fwd_f32_kernel(const float* __restrict__ x, const int32_t* __restrict__ nbr
     }
     for (int st = 0; st < steps; ++st) {
         asm volatile("cp.async.wait_group %0;" ::"n"(F_STAGES - 2) : "memory");
-        __syncthreads();       // step st has landed for every thread; the buffer refilled below is no longer read
+        if (F_THREADS == 32) __syncwarp(); else __syncthreads();   // step st has landed for every thread; the buffer refilled below is no longer read
         if (st + F_STAGES - 1 < steps) load_stage((st + F_STAGES - 1) % F_STAGES);
         asm volatile("cp.async.commit_group;" ::: "memory");
         const float* as = sm.a[st % F_STAGES];
         const float* bs = sm.b[st % F_STAGES];
 #pragma unroll
         for (int c4 = 0; c4 < F_BK; c4 += 4) {
-            float4 av[8];
+            float4 av[RPT];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) av[i] = *reinterpret_cast<const float4*>(as + (ty + 8 * i) * F_ASTR + c4);
+            for (int i = 0; i < RPT; ++i) av[i] = *reinterpret_cast<const float4*>(as + (ty + TYN * i) * F_ASTR + c4);
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
                 const float4 bv = *reinterpret_cast<const float4*>(bs + (c4 + cc) * F_BN + tx * 4);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
+                for (int i = 0; i < RPT; ++i) {
                     const float a = cc == 0 ? av[i].x : cc == 1 ? av[i].y : cc == 2 ? av[i].z : av[i].w;
                     acc[i][0] = fmaf(a, bv.x, acc[i][0]);
                     acc[i][1] = fmaf(a, bv.y, acc[i][1]);
@@ -145,8 +158,8 @@ conv_fwd_f32_kernel(const float* __restrict__ x, const int32_t* __restrict__ nbr
         float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
         if (bias != nullptr && col < cout) b4 = __ldg(reinterpret_cast<const float4*>(bias + col));
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const long row = row0 + ty + 8 * i;
+        for (int i = 0; i < RPT; ++i) {
+            const long row = row0 + ty + TYN * i;
             if (row < n && col < cout)
                 *reinterpret_cast<float4*>(out + row * cout + col) =
                     make_float4(acc[i][0] + b4.x, acc[i][1] + b4.y, acc[i][2] + b4.z, acc[i][3] + b4.w);
@@ -157,8 +170,8 @@ conv_fwd_f32_kernel(const float* __restrict__ x, const int32_t* __restrict__ nbr
     __syncthreads();                              // everyone is done with the stage ring: park the tile in it
     float* red = reinterpret_cast<float*>(f_smem_raw);
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-        *reinterpret_cast<float4*>(red + (ty + 8 * i) * F_RSTR + tx * 4) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    for (int i = 0; i < RPT; ++i)
+        *reinterpret_cast<float4*>(red + (ty + TYN * i) * F_RSTR + tx * 4) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     {
@@ -190,10 +203,12 @@ conv_fwd_f32_kernel(const float* __restrict__ x, const int32_t* __restrict__ nbr
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
-template <int G>
-static int launch_fwd_f32(const ConvArgs& p, int tiles_m, int tiles_n, cudaStream_t s) {
-    auto kern = conv_fwd_f32_kernel<G>;
-    const size_t smem = sizeof(FwdSmem);
+template <int G, int F_BM, int F_BN, int RPT>
+static int launch_fwd_f32(const ConvArgs& p, cudaStream_t s) {
+    auto kern = conv_fwd_f32_kernel<G, F_BM, F_BN, RPT>;
+    const int tiles_m = (int)((p.n + F_BM - 1) / F_BM), tiles_n = (p.cout + F_BN - 1) / F_BN;
+    constexpr int F_THREADS = F_BM * F_BN / (4 * RPT);
+    const size_t smem = sizeof(FwdSmem<F_BM, F_BN>);
     static bool attr_set[64] = {false};
     int dev = 0;
     SV_CUDA(cudaGetDevice(&dev));
@@ -226,16 +241,17 @@ bool simt_fwd_f32_supported(const ConvArgs& p) {
 
 // fp32 forward; the caller has checked simt_fwd_f32_supported().
 int simt_fwd_f32(const ConvArgs& p, cudaStream_t s) {
-    const int tiles_m = (int)((p.n + F_BM - 1) / F_BM), tiles_n = (p.cout + F_BN - 1) / F_BN;
-    const long tiles = (long)tiles_m * tiles_n;
-    // split the taps over a cluster while that brings more SMs into play (148 on a B200, a few CTAs each)
+    const long tiles = ((p.n + 63) / 64) * ((p.cout + 63) / 64);
+    if (tiles >= 2 * 148) return launch_fwd_f32<1, 64, 64, 8>(p, s);
+    // small call: the K steps split over a cluster while that brings more SMs into play (148 on a B200, a few
+    // CTAs each)
     int g = 1;
-    while (g < 8 && tiles * g < 2 * 148 && 2 * g <= p.kk) g *= 2;
+    while (g < 8 && tiles * g < 2 * 148) g *= 2;
     switch (g) {
-        case 1: return launch_fwd_f32<1>(p, tiles_m, tiles_n, s);
-        case 2: return launch_fwd_f32<2>(p, tiles_m, tiles_n, s);
-        case 4: return launch_fwd_f32<4>(p, tiles_m, tiles_n, s);
-        default: return launch_fwd_f32<8>(p, tiles_m, tiles_n, s);
+        case 1: return launch_fwd_f32<1, 64, 64, 8>(p, s);
+        case 2: return launch_fwd_f32<2, 64, 64, 8>(p, s);
+        case 4: return launch_fwd_f32<4, 64, 64, 8>(p, s);
+        default: return launch_fwd_f32<8, 64, 64, 8>(p, s);
     }
 }
 
