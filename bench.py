@@ -243,6 +243,9 @@ def main():
                     help="backbone: forward of the ViT-B sparse-adapter backbone on 160-frame clips (secondary line); "
                          "configs: the other benchmark configurations (--configs 1,3,4), one JSON line each")
     ap.add_argument("--configs", default="1,3,4")
+    ap.add_argument("--backbone-schedule", default="primary", choices=["primary", "reference"],
+                    help="primary: 30 %% keep after block 3 only; reference: the reference's ViT-B schedule, keep 0.6 after "
+                         "blocks 3, 6 and 9 (vit_sparse_adapter_poguise.py:1503-1504)")
     ap.add_argument("--backbone-train", action="store_true",
                     help="with --workload backbone: one training step (forward, backward to the adapters, AdamW) per step")
     ap.add_argument("--kernel-case", default=None, choices=["fwd", "dgrad", "wgrad", "table"],
@@ -568,7 +571,8 @@ def main():
 
     # Steps alternate between two streams, so the copies in of one step overlap the copies out of the one before
     # (with N > 1 a single stream keeps the ranks' collectives in one order).
-    step_streams = [torch.cuda.Stream(device=dev) for _ in range(2 if world == 1 else 1)]
+    n_step_streams = int(os.environ.get("SVTAD_BENCH_E2E_STREAMS", "2")) if world == 1 else 1
+    step_streams = [torch.cuda.Stream(device=dev) for _ in range(n_step_streams)]
     for i in range(3):          # eager warm-up: allocator pools, cached parameter copies, the library's side stream
         with torch.cuda.stream(step_streams[0]):
             fork_join(i)
@@ -642,6 +646,51 @@ def main():
         assert torch.equal(out_h[chk][ki]["gx"].to(dev), gx_ref), "e2e input gradient differs from the resident path"
     e2e_ms = sorted(block_ms)[len(block_ms) // 2]
     e2e_value = world * tokens_step * e2e_steps / (e2e_ms * 1e-3)
+
+    # what the host link gives in this run: pinned copies of the step's volume, each direction alone and both at once
+    def copy_rate(do_h2d, do_d2h, reps=6):
+        hb = torch.empty(h2d, dtype=torch.uint8).pin_memory()
+        db = torch.empty(h2d, dtype=torch.uint8, device=dev)
+        hb2 = torch.empty(d2h, dtype=torch.uint8).pin_memory()
+        db2 = torch.empty(d2h, dtype=torch.uint8, device=dev)
+        s1, s2 = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        s1.wait_stream(torch.cuda.current_stream()); s2.wait_stream(torch.cuda.current_stream())
+        for _ in range(reps):
+            if do_h2d:
+                with torch.cuda.stream(s1):
+                    db.copy_(hb, non_blocking=True)
+            if do_d2h:
+                with torch.cuda.stream(s2):
+                    hb2.copy_(db2, non_blocking=True)
+        torch.cuda.current_stream().wait_stream(s1); torch.cuda.current_stream().wait_stream(s2)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+    ms_h, ms_d, ms_both = copy_rate(True, False), copy_rate(False, True), copy_rate(True, True)
+    link = {"h2d_alone_GBs": h2d / (ms_h * 1e-3) / 1e9, "d2h_alone_GBs": d2h / (ms_d * 1e-3) / 1e9,
+            "both_at_once_ms_per_step_volume": ms_both,
+            "achieved_h2d_GBs": h2d / (e2e_ms / e2e_steps * 1e-3) / 1e9, "achieved_d2h_GBs": d2h / (e2e_ms / e2e_steps * 1e-3) / 1e9,
+            "note": "pinned copies of one step's bytes measured in this run; 'both at once' is the floor of an e2e step"}
+    if world > 1:
+        link["note"] += "; with N > 1 all ranks share one host's memory and PCIe root, which bounds the e2e number"
+
+    # the same public-API calls issued eagerly, no CUDA graph (what a training loop pays per step on the host)
+    eager_ms = None
+    if world == 1:
+        with torch.cuda.stream(step_streams[0]):
+            for i in range(2):
+                fork_join(i)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(step_streams[0])
+            for i in range(10):
+                fork_join(i)
+            b.record(step_streams[0])
+            b.synchronize()
+            eager_ms = a.elapsed_time(b) / 10
     sampler.stop_flag = True
     assert ops.device_error() == 0, "a bounded wait inside a tensor-core kernel gave up"
 
@@ -672,7 +721,8 @@ def main():
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
                     "stat": f"median of {E2E_BLOCKS} blocks of {e2e_steps} steps",
                     "launch": "cuda_graph of the public-API calls" if e2e_graphs is not None else "eager",
-                    "block_ms_per_step": [round(m / e2e_steps, 4) for m in block_ms]},
+                    "block_ms_per_step": [round(m / e2e_steps, 4) for m in block_ms],
+                    "host_link": link, "eager_ms_per_step": eager_ms},
             "gpu_launches": launches_per_step * args.steps,
             "roofline": roofline, "cpu_baseline": cpu, "reference_cuda": ref_cuda,
             "clocks": sampler.summary(),
@@ -701,7 +751,10 @@ def backbone_case(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     torch.manual_seed(5 + rank)
-    model = SparseAdapterViT().to(dev).eval()
+    keep_rates = None
+    if args.backbone_schedule == "reference":
+        keep_rates = [1.0, 1.0, 1.0, 0.6, 1.0, 1.0, 0.6, 1.0, 1.0, 0.6, 1.0, 1.0]
+    model = SparseAdapterViT(keep_rates=keep_rates).to(dev).eval()
     for blk in model.blocks:
         torch.nn.init.normal_(blk.adapter.up_proj.weight, std=0.02)
     clips = [torch.randn(1, 3, 160, 224, 224, device=dev) for _ in range(2)]
@@ -757,7 +810,8 @@ def backbone_case(args):
                           "unit": "clips/s", "n_gpus": world, "steps": steps, "warmup": warm, "ms_per_step": ms / steps,
                           "higher_is_better": True, "scaling": "weak", "dtype": "bf16", "data": "synthetic",
                           "config": {"workload": f"ViT-B/16 sparse-adapter backbone {what}, 3x160x224x224 clips, "
-                                                 "15680 tokens + CLS, adapters 768->192->768 with SparseConv2D 3x3, keep 30 % after block 3"},
+                                                 "15680 tokens + CLS, adapters 768->192->768 with SparseConv2D 3x3, " +
+                                                 ("keep 30 % after block 3" if keep_rates is None else "keep 0.6 after blocks 3, 6, 9 (reference schedule)")},
                           "out_shape": list(out.shape)}))
     if world > 1:
         torch.cuda.synchronize()

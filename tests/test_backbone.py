@@ -86,3 +86,58 @@ def test_adapter_gradients_match_dense_restatement_fp32():
         scale = a.abs().max().item()
         assert scale > 0, n
         assert (a - b).abs().max().item() / scale < 2e-3, n
+
+
+@pytest.mark.gpu
+def test_full_size_three_round_schedule_tables_bit_for_bit():
+    """The reference's ViT-B schedule at the benchmark's clip size: 80 slices of 14x14 tokens per clip (15 680), keep
+    0.6 after blocks 3, 6 and 9 (15 680 -> 9 408 -> 5 645 -> 3 387 per clip,
+    vit_sparse_adapter_poguise.py:1503-1504).  Table maintenance by the CUDA kernels (one fused select + remap kernel
+    per round) must equal the reference's tensor ops restated in torch - indices and tables, bit for bit - and every
+    table must stay symmetric with the centre tap pointing at the row itself."""
+    from eccv26_tad_b200.backbone import _torch_remap
+    from eccv26_tad_b200.neighbor_table import get_initial_neighbor_indices, num_keep_tokens, select_and_update
+    B, T, h, w = 2, 80, 14, 14
+    g = torch.Generator().manual_seed(77)
+    table_a = get_initial_neighbor_indices(h, w, T, "cuda", B)
+    table_b = table_a.clone()
+    n = T * h * w
+    expect = [9408, 5645, 3387]
+    for rnd in range(3):
+        scores = torch.rand(B, n, generator=g).cuda()            # distinct with probability ~1: no tie at a threshold
+        k = num_keep_tokens(0.6, n)
+        assert k == expect[rnd]
+        idx_a, table_a = select_and_update(scores, table_a, k)
+        idx_b = torch.topk(scores, k, dim=1, largest=True)[1].sort(dim=1)[0]
+        table_b = _torch_remap(table_b, idx_b)
+        assert torch.equal(idx_a, idx_b) and torch.equal(table_a, table_b)
+        flat = table_a.reshape(-1, 9)
+        rows = torch.arange(flat.shape[0], device="cuda", dtype=torch.int32)
+        assert torch.equal(flat[:, 4], rows)
+        for kk in range(9):                                      # entry (i, k) = j  <=>  entry (j, 8 - k) = i
+            j = flat[:, kk].long()
+            ok = j >= 0
+            assert torch.equal(flat[j[ok], 8 - kk], rows[ok])
+        n = k
+
+
+@pytest.mark.gpu
+def test_full_size_backbone_sparse_vs_dense_bf16():
+    """One full-size clip (3 x 160 x 224 x 224, ViT-B, adapter width 192, 30 % keep after block 3) under bf16 autocast:
+    the product path against the dense scatter -> conv2d -> gather restatement with the same weights."""
+    torch.manual_seed(1)
+    dense = SparseAdapterViT(conv_impl="dense", table_impl="torch")
+    for blk in dense.blocks:
+        torch.nn.init.normal_(blk.adapter.up_proj.weight, std=0.02)
+    dense = dense.cuda().eval()
+    sparse = SparseAdapterViT(conv_impl="svtad", table_impl="svtad").cuda().eval()
+    sparse.load_state_dict(dense.state_dict())
+    video = torch.randn(1, 3, 160, 224, 224, device="cuda")
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        a = dense(video).float()
+        b = sparse(video).float()
+    assert a.shape == (1, 768, 81)
+    # both models select once, in block 3; up to there they run the same kernels on the same bits except for the
+    # adapters' convolution, whose bf16 rounding can flip a near-tie of the top-k: compare where it matters least
+    err = (a - b).abs().mean().item() / a.abs().mean().item()
+    assert err < 5e-2, err

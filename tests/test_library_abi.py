@@ -196,3 +196,18 @@ def test_reference_wrapper_binds_to_the_shim_when_built():
     ours = list(inspect.signature(SparseConv2d.__init__).parameters)
     assert ours[:len(theirs)] == theirs
     assert list(ref.SparseConv2d(8, 12).state_dict()) == list(SparseConv2d(8, 12).state_dict())
+
+
+def test_top_level_opentad_sparse_ops_module():
+    """``import opentad_sparse_ops`` (the module the reference wrapper looks for, built by the reference's setup.py as
+    a CUDA extension) resolves to this package's callables without any install() call; setup.py ships it as a
+    top-level module beside the package."""
+    import importlib
+    import sys
+    sys.modules.pop("opentad_sparse_ops", None)
+    mod = importlib.import_module("opentad_sparse_ops")
+    from eccv26_tad_b200 import opentad_sparse_ops as shim
+    for name in ("fwd", "bwd_in", "bwd_w", "implicit_gemm_fwd_v2", "implicit_gemm_fwd_v2_chunked"):
+        assert getattr(mod, name) is getattr(shim, name)
+    text = open(os.path.join(ROOT, "setup.py")).read()
+    assert 'py_modules=["opentad_sparse_ops"]' in text and "libsvtad.so" in text
