@@ -160,33 +160,57 @@ int tc_pick_bn(int cn, long m_tiles) {
     return best;
 }
 
-// wgrad work split: (pairs of 64-channel blocks) x (column blocks) x (splits over tokens)
+// wgrad work split: (pairs of 64-channel blocks) x (column blocks of width BN) x (splits over tokens).
+// One CTA runs per SM, so a candidate (BN, splits) costs
+//   (waves over the SMs) x (64-token steps per CTA + fixed cost) x (cycles per step at that BN)
+// plus the trip of the fp32 partials through memory (written by the main kernel, read by the reduction).
+// Cycles per step and the partials' rate are what these kernels were measured at on a B200.
 WgradPlan tc_wgrad_plan(int64_t n, int cin, int cout, int kk) {
-    WgradPlan pl;
-    pl.bn = (cout <= 256) ? cout : (cout % 256 == 0 ? 256 : (cout % 192 == 0 ? 192 : (cout % 128 == 0 ? 128 : 64)));
-    pl.n_nblk = cout / pl.bn;
-    int nblocks = kk * (cin / 64);
-    pl.n_pairs = (nblocks + 1) / 2;
-    pl.ones_block = nblocks & 1;
-    long ctas = (long)pl.n_pairs * pl.n_nblk;
+    const int nblocks = kk * (cin / 64);
     const long sms = tc_num_sms();
     long max_by_rows = (n + 2 * STAGE_K - 1) / (2 * STAGE_K);
     if (max_by_rows < 1) max_by_rows = 1;
     if (max_by_rows > 64) max_by_rows = 64;
-    // minimise (waves over the SMs) x (tokens per split + fixed cost), ties to fewer splits
-    long s = 1;
-    double best = 0;
-    for (long c = 1; c <= max_by_rows; ++c) {
-        long waves = (ctas * c + sms - 1) / sms;
-        double cost = (double)waves * (double)((n + c - 1) / c + 4 * STAGE_K);
-        if (c == 1 || cost < best * 0.98) { best = cost; s = c; }
+    int forced_bn = 0;
+    if (const char* e = getenv("SVTAD_TC_WGRAD_BN")) forced_bn = atoi(e);
+    long forced_s = 0;
+    if (const char* e = getenv("SVTAD_TC_WGRAD_SPLITS")) forced_s = atol(e);
+    const int cand[4] = {256, 192, 128, 64};
+    const double step_cycles[4] = {650.0, 584.0, 450.0, 400.0};
+    // partials are written once and read once: from L2 while they fit beside the operands, else from memory
+    const double partial_cycles_l2 = 2.0 * 1.9e9 / 12.0e12, partial_cycles_mem = 2.0 * 1.9e9 / 4.0e12;
+    WgradPlan best;
+    best.bn = 0;
+    double best_cost = 0;
+    for (int ci = 0; ci < 4; ++ci) {
+        const int bn = cand[ci];
+        if (cout % bn != 0) continue;
+        if (bn < 192 && best.bn != 0 && forced_bn == 0) continue;      // narrow blocks only when no wide one divides cout
+        if (forced_bn > 0 && bn != forced_bn && cout % forced_bn == 0) continue;
+        WgradPlan pl;
+        pl.bn = bn;
+        pl.n_nblk = cout / bn;
+        pl.n_pairs = (nblocks + 1) / 2;
+        pl.ones_block = nblocks & 1;
+        const long ctas = (long)pl.n_pairs * pl.n_nblk;
+        for (long c = 1; c <= max_by_rows; ++c) {
+            if (forced_s > 0 && c != (forced_s < max_by_rows ? forced_s : max_by_rows)) continue;
+            const long tps = ((n + c - 1) / c + STAGE_K - 1) / STAGE_K * STAGE_K;
+            const long splits = (n + tps - 1) / tps;
+            const long waves = (ctas * splits + sms - 1) / sms;
+            const double steps = (double)tps / STAGE_K + 12.0;          // + set-up, first operands, drain
+            const double partial_bytes = (double)splits * kk * cin * cout * sizeof(float);
+            const double cost = (double)waves * steps * step_cycles[ci] +
+                                partial_bytes * (partial_bytes < 48e6 ? partial_cycles_l2 : partial_cycles_mem);
+            if (best.bn == 0 || cost < best_cost * 0.98) {
+                best = pl;
+                best.tokens_per_split = tps;
+                best.splits = (int)splits;
+                best_cost = cost;
+            }
+        }
     }
-    const char* e = getenv("SVTAD_TC_WGRAD_SPLITS");
-    if (e != nullptr && *e && atoi(e) > 0) s = atoi(e) < max_by_rows ? atoi(e) : max_by_rows;
-    long tps = ((n + s - 1) / s + STAGE_K - 1) / STAGE_K * STAGE_K;
-    pl.tokens_per_split = tps;
-    pl.splits = (int)((n + tps - 1) / tps);
-    return pl;
+    return best;
 }
 
 static size_t plan_bytes(const WgradPlan& pl, int64_t n, int cin, int cout, int kk) {
