@@ -170,8 +170,11 @@ int svtad_conv_bwd(const void* gy, const void* x, const int32_t* nbr, const void
  * (no cudaMalloc / cudaFree, no allocating library routine).
  *   - Limit: problems with svtad_workspace_bytes(SVTAD_OP_WGRAD, ...) > SVTAD_STATIC_WS_BYTES are
  *     refused with SVTAD_ERR_WORKSPACE (C = 192 and 256 at 3x3 fit; C = 1024 does not).
- *   - The first call on a device looks the array's address up (cudaGetSymbolAddress, with that
- *     device current); make that first call before any stream capture.
+ *   - "Allocates nothing" holds from the second call of a kind on.  The first call on a device looks the
+ *     array's address up (cudaGetSymbolAddress, with that device current), and the first launch of each
+ *     kernel variant (one per column-block width and dtype family, plus the reduction) makes the CUDA
+ *     runtime load it, which may allocate inside the driver.  So make one call per shape and dtype that
+ *     will be used during start-up, before the phase in which nothing may allocate.
  *   - All calls on a device share the array and it keeps the previous call's contents.  Nothing in
  *     it needs clearing between calls, but two calls that overlap on the GPU (different streams)
  *     race on it: keep them on one stream or order them with events.
