@@ -53,8 +53,9 @@ FALLBACK_TFLOPS = 1590.0
 FALLBACK_HBM = 6650.0
 METRIC = "SparseConv2D retained tokens/sec fwd+bwd at keep 10-55%"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu captures summarised under profiles/
-# (226 560-row case, C=192), divided by the rows of that launch; traffic grows in proportion to the rows
-NCU_DRAM_BYTES_PER_ROW = {"fwd": 136.85e6 / 226560, "dgrad": 137.57e6 / 226560, "wgrad": 241.24e6 / 226560}
+# (the benchmark's largest layer: 17 280 rows, C=192), divided by the rows of that launch; traffic grows in
+# proportion to the rows
+NCU_DRAM_BYTES_PER_ROW = {"fwd": 7.97e6 / 17280, "dgrad": 7.97e6 / 17280, "wgrad": 13.93e6 / 17280}
 
 
 def flops_pass(n):
@@ -804,6 +805,39 @@ def backbone_case(args):
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    glue = None
+    if rank == 0 and not train:
+        # the adapter's glue around the op (GELU on down_proj's output, the copy that drops the special tokens, the
+        # concatenation that puts them back), timed by itself at every adapter's token count
+        counts = []
+        hooks = [blk.adapter.register_forward_pre_hook(lambda _m, inp: counts.append(inp[0].shape[1]))
+                 for blk in model.blocks]
+        step(clips[0])
+        for h_ in hooks:
+            h_.remove()
+        hidden = model.blocks[0].adapter.down_proj.out_features
+
+        def timed(fn, reps=20):
+            fn()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / reps * 1e3
+        tot = {"gelu_us": 0.0, "slice_copy_us": 0.0, "cat_us": 0.0}
+        for ntok in counts:
+            z = torch.randn(1, ntok, hidden, device=dev, dtype=torch.bfloat16)
+            conv = torch.randn(1, ntok - 1, hidden, device=dev, dtype=torch.bfloat16)
+            tot["gelu_us"] += timed(lambda: torch.nn.functional.gelu(z))
+            tot["slice_copy_us"] += timed(lambda: z[:, 1:].contiguous())
+            tot["cat_us"] += timed(lambda: torch.cat([z[:, :1], conv], dim=1))
+        per_clip = sum(tot.values())
+        glue = dict({k: round(v, 1) for k, v in tot.items()}, per_clip_us=round(per_clip, 1),
+                    share_of_forward=round(per_clip * 1e-3 / (ms / steps), 4), adapters=len(counts),
+                    what="eager torch kernels around SparseConv2d in every adapter, summed over the clip's adapters")
     if rank == 0:
         what = "training step (forward, backward to the adapters, AdamW)" if train else "forward"
         print(json.dumps({"metric": f"sparse-adapter ViT-B backbone {what}, clips/s", "value": world * steps / (ms * 1e-3),
@@ -812,7 +846,7 @@ def backbone_case(args):
                           "config": {"workload": f"ViT-B/16 sparse-adapter backbone {what}, 3x160x224x224 clips, "
                                                  "15680 tokens + CLS, adapters 768->192->768 with SparseConv2D 3x3, " +
                                                  ("keep 30 % after block 3" if keep_rates is None else "keep 0.6 after blocks 3, 6, 9 (reference schedule)")},
-                          "out_shape": list(out.shape)}))
+                          "adapter_glue": glue, "out_shape": list(out.shape)}))
     if world > 1:
         torch.cuda.synchronize()
         dist.barrier()
