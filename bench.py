@@ -326,7 +326,7 @@ def main():
     allreduce_kind = buckets[0].kind
     if world > 1 and want_peer and buckets[0].kind == "nccl":
         sys.stderr.write(f"[bench] peer-memory all-reduce unavailable ({getattr(buckets[0], 'fallback_reason', '?')}); using NCCL\n")
-    comm = torch.cuda.Stream(device=dev)
+    comm = torch.cuda.Stream(device=dev, priority=-1 if (world > 1 and os.environ.get("SVTAD_BENCH_STREAM_PRIORITY", "1") != "0") else 0)
     gw_buf, gb_buf = gw_bufs[0], gb_bufs[0]
     launches_per_step = 0
 
@@ -335,7 +335,11 @@ def main():
     y_bufs = [torch.empty(it["n"], C, dtype=torch.bfloat16, device=dev) for it in host_sets[0]]
     gx_bufs = [torch.empty(it["n"], C, dtype=torch.bfloat16, device=dev) for it in host_sets[0]]
     ws_l = [torch.empty(ws_bytes, dtype=torch.uint8, device=dev) for _ in KEEPS]
-    sides = [torch.cuda.Stream(device=dev) for _ in KEEPS]
+    # With N > 1 the weight gradients and the exchange that follows them are the step's critical path (everything
+    # else only has to be done by the end of the step), so their streams get the higher priority: their CTAs are
+    # placed first whenever an SM has room, and the exchange starts early enough to hide behind forward / dgrad.
+    hi = -1 if (world > 1 and os.environ.get("SVTAD_BENCH_STREAM_PRIORITY", "1") != "0") else 0
+    sides = [torch.cuda.Stream(device=dev, priority=hi) for _ in KEEPS]
     lanes = [torch.cuda.Stream(device=dev) for _ in KEEPS]
 
     def raw_step(dk, stream=None, count=False):
@@ -346,7 +350,10 @@ def main():
         runs while the rest of the step still computes."""
         nl = 0
         cur = torch.cuda.current_stream()
-        early_wgrad = world > 1 and not args.ar_per_layer and args.layer_streams
+        early_wgrad = (world > 1 and not args.ar_per_layer and args.layer_streams
+                       and os.environ.get("SVTAD_BENCH_EARLY_WGRAD", "1") != "0")
+        if os.environ.get("SVTAD_BENCH_EARLY_WGRAD") == "force":
+            early_wgrad = True
 
         def wgrad(li, it, st):
             ops._lib.check(lib.svtad_conv_wgrad(it["gy"].data_ptr(), it["x"].data_ptr(), it["table"].data_ptr(),
@@ -360,7 +367,7 @@ def main():
                 comm.wait_stream(sides[li])
             with torch.cuda.stream(comm):
                 buckets[0].all_reduce()
-            nl += 1
+            nl += 1 if world > 1 else 0
         for li, it in enumerate(dk):
             n = it["n"]
             main = lanes[li] if args.layer_streams else cur
@@ -387,12 +394,11 @@ def main():
         if args.layer_streams:
             for li in range(len(dk)):
                 cur.wait_stream(lanes[li])
-        if world > 1:
-            if args.ar_per_layer or early_wgrad:
-                cur.wait_stream(comm)
-            else:
-                buckets[0].all_reduce()
-                nl += 1
+        if early_wgrad or (world > 1 and args.ar_per_layer):
+            cur.wait_stream(comm)
+        elif world > 1:
+            buckets[0].all_reduce()
+            nl += 1
         return nl
 
     stream = torch.cuda.Stream(device=dev)
@@ -514,6 +520,15 @@ def main():
         "whole_step_frac": 3 * dom_flops / (ms_total / args.steps * 1e-3) / 1e12 / peak_tf,
     }
 
+    if os.environ.get("SVTAD_BENCH_VALUE_ONLY"):       # a short line for sweeps: the resident step only
+        if rank == 0:
+            print(json.dumps({"n_gpus": world, "ms_per_step": ms_total / args.steps, "sweep_line": True,
+                              "config": {"allreduce": allreduce_kind}}))
+            sys.stdout.flush()
+        if world > 1:
+            torch.cuda.synchronize()
+            dist.barrier()
+        os._exit(0)
     # ---------------------------------------------------------------- e2e through the public API, host buffers
     # One SparseConv2d per keep rate (three adapter layers with the same initial weights), each on its own
     # stream: copy in -> table -> forward -> backward -> copy out are ordered inside a layer's stream, and the

@@ -20,14 +20,21 @@
 // (svtad_device_error), stops and returns; the bucket entries it had not reached stay as they were.  The call
 // number lives in device memory and is advanced by the kernel itself, so a CUDA graph can replay the launch;
 // flags are never reset (a stale unit carries an older number).
+#include <cstdlib>
+#include <mutex>
+#include <set>
+#include <utility>
+
 #include "common.cuh"
 
 namespace svtad {
 
 int* tc_error_ptr();     // the library's device error word (conv_tc.cu)
 
-constexpr int AR_THREADS = 256;        // small CTAs: they fit beside a compute kernel's CTA on an SM
-constexpr int AR_MAX_CTAS = 128;
+// Small CTAs: four warps, one per SM sub-partition, so that a CTA fits into the registers a convolution CTA leaves
+// free (a 9-warp CTA at 136 registers leaves 3 328 registers in its fullest sub-partition: one warp of this kernel).
+constexpr int AR_THREADS = 128;
+constexpr int AR_MAX_CTAS = 256;
 constexpr int AR_MAX_RANKS = 16;
 constexpr long long AR_DEFAULT_LIMIT = 2000000000ll;     // about a second
 
@@ -66,9 +73,13 @@ __device__ __forceinline__ void push_unit(void* dst, uint4 d, unsigned e) {
     st_volatile_v4(static_cast<char*>(dst) + 16, make_uint4(d.z, e, d.w, e));
 }
 // Waits (bounded) until the 32-byte unit at `src` carries call number e; false when the limit ran out.
+// After a miss the thread sleeps (`backoff` ns, doubling up to 16x) before it looks again: the pollers read this
+// GPU's own memory through L2, and thousands of them spinning flat out take bandwidth from the kernels that run
+// beside the exchange.
 __device__ __forceinline__ bool poll_unit(const void* src, unsigned e, uint4& d, long long limit, int* err, int code,
-                                          volatile int* s_abort) {
+                                          volatile int* s_abort, unsigned backoff) {
     long long t0 = 0;
+    unsigned nap = backoff;
     for (unsigned spin = 0;; ++spin) {
         const uint4 lo = ld_volatile_v4(src);
         const uint4 hi = ld_volatile_v4(static_cast<const char*>(src) + 16);
@@ -77,6 +88,10 @@ __device__ __forceinline__ bool poll_unit(const void* src, unsigned e, uint4& d,
             return true;
         }
         if (spin == 0) t0 = clock64();
+        if (nap) {
+            __nanosleep(nap);
+            if (nap < backoff * 16u) nap *= 2u;
+        }
         if ((spin & 7u) == 7u) {
             if (*s_abort) return false;
             if (clock64() - t0 > limit) {
@@ -92,7 +107,7 @@ __device__ __forceinline__ bool poll_unit(const void* src, unsigned e, uint4& d,
 // [bucket: n_unit * 16 B][in: world rows of n_unit / world units * 32 B][out: n_unit units * 32 B].
 // Returns false when a wait ran out of time (the error word has been set).
 __device__ bool ar_rank_body(void* const* bufs, int rank, int world, long n_unit, size_t stage_off, unsigned* epoch, int fp16_i,
-                             long long limit, int* err, int cta, int n_ctas, volatile int* s_abort) {
+                             long long limit, int* err, int cta, int n_ctas, volatile int* s_abort, unsigned backoff) {
     const int tid = threadIdx.x;
     const bool fp16 = fp16_i != 0;
     const unsigned e = epoch[cta] + 1u;          // number of this call; the same on every rank and CTA
@@ -118,7 +133,7 @@ __device__ bool ar_rank_body(void* const* bufs, int rank, int world, long n_unit
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (int p = 0; p < world; ++p) {
             uint4 d = own;
-            if (p != rank) ok = ok && poll_unit(mine + in_off + ((size_t)p * S + j) * 32, e, d, limit, err, 71, s_abort);
+            if (p != rank) ok = ok && poll_unit(mine + in_off + ((size_t)p * S + j) * 32, e, d, limit, err, 71, s_abort, backoff);
             if (!ok) break;
             acc8(acc, d, fp16);
         }
@@ -135,7 +150,7 @@ __device__ bool ar_rank_body(void* const* bufs, int rank, int world, long n_unit
         const int p = (int)(u / S);
         if (p == rank) continue;
         uint4 d;
-        ok = poll_unit(mine + out_off + (size_t)u * 32, e, d, limit, err, 72, s_abort);
+        ok = poll_unit(mine + out_off + (size_t)u * 32, e, d, limit, err, 72, s_abort, backoff);
         if (ok) *reinterpret_cast<uint4*>(mine + u * 16) = d;
     }
     __syncthreads();
@@ -146,23 +161,23 @@ __device__ bool ar_rank_body(void* const* bufs, int rank, int world, long n_unit
 
 struct ArPeers { void* p[AR_MAX_RANKS]; };
 
-__global__ void __launch_bounds__(AR_THREADS, 3)
+__global__ void __launch_bounds__(AR_THREADS, 8)
 allreduce_twoshot_kernel(ArPeers peers, int rank, int world, long n_unit, size_t stage_off, unsigned* epoch, int fp16,
-                         long long limit, int* err) {
+                         long long limit, int* err, unsigned backoff) {
     __shared__ int s_flag;
-    ar_rank_body(peers.p, rank, world, n_unit, stage_off, epoch, fp16, limit, err, blockIdx.x, gridDim.x, &s_flag);
+    ar_rank_body(peers.p, rank, world, n_unit, stage_off, epoch, fp16, limit, err, blockIdx.x, gridDim.x, &s_flag, backoff);
 }
 
 // All ranks in ONE launch on one GPU (blockIdx.y = rank): the same protocol with every "peer" buffer local.  The
 // CTAs of different ranks wait for one another, so the launch is cooperative (all of them resident).  For tests on
 // a machine with fewer GPUs than ranks.
-__global__ void __launch_bounds__(AR_THREADS, 3)
+__global__ void __launch_bounds__(AR_THREADS, 8)
 allreduce_twoshot_emulated_kernel(ArPeers peers, int world, long n_unit, size_t stage_off, unsigned* epochs, int fp16,
-                                  long long limit, int* err) {
+                                  long long limit, int* err, unsigned backoff) {
     __shared__ int s_flag;
     const int rank = blockIdx.y;
     ar_rank_body(peers.p, rank, world, n_unit, stage_off, epochs + rank * AR_MAX_CTAS, fp16, limit, err, blockIdx.x,
-                 gridDim.x, &s_flag);
+                 gridDim.x, &s_flag, backoff);
 }
 
 static int ar_check(const char* who, void* const* peer_bufs, int rank, int world, int64_t n_elems, int dtype,
@@ -182,12 +197,39 @@ static int ar_check(const char* who, void* const* peer_bufs, int rank, int world
     return SVTAD_OK;
 }
 
+// SVTAD_ALLREDUCE_CTAS / SVTAD_ALLREDUCE_BACKOFF_NS, read once: every rank must run with the same values
+static int ar_env(const char* name, int lo, int hi, int dflt) {
+    const char* e = getenv(name);
+    if (e == nullptr || !*e) return dflt;
+    int v = atoi(e);
+    return v < lo ? lo : (v > hi ? hi : v);
+}
+// Default 128 CTAs: measured beside the convolution kernels on two B200s, a 2 MB bucket's step took 0.1103 / 0.1093 /
+// 0.1098 / 0.1136 ms with 256 / 128 / 64 / 32 CTAs.
+static int ar_max_ctas() { static const int v = ar_env("SVTAD_ALLREDUCE_CTAS", 1, AR_MAX_CTAS, 128); return v; }
+static unsigned ar_backoff() { static const int v = ar_env("SVTAD_ALLREDUCE_BACKOFF_NS", 0, 4096, 0); return (unsigned)v; }
+
+// The exchange is meant to run beside the convolution kernels, whose CTAs take nearly all of an SM's shared memory.
+// An SM runs kernels of one shared-memory / L1 split at a time, so this kernel asks for the same split (all shared)
+// although it uses four bytes of it; otherwise its CTAs wait for SMs without a convolution CTA.  Once per device.
+static int ar_prefer_shared(const void* kern) {
+    static std::mutex mu;
+    static std::set<std::pair<const void*, int>> done;
+    int dev = 0;
+    SV_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> hold(mu);
+    if (done.count({kern, dev})) return SVTAD_OK;
+    SV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    done.insert({kern, dev});
+    return SVTAD_OK;
+}
+
 static int ar_ctas(int64_t n_unit, int world) {
-    // about four 16-byte units of the bucket per thread, within [1, AR_MAX_CTAS]
+    // about four 16-byte units of the bucket per thread, within [1, the cap]
     (void)world;
     long c = (n_unit + 4 * AR_THREADS - 1) / (4 * AR_THREADS);
     if (c < 1) c = 1;
-    if (c > AR_MAX_CTAS) c = AR_MAX_CTAS;
+    if (c > ar_max_ctas()) c = ar_max_ctas();
     return (int)c;
 }
 
@@ -210,8 +252,12 @@ extern "C" int svtad_allreduce_sum(void* const* peer_bufs, int rank, int world, 
     const long long limit = wait_limit_cycles > 0 ? wait_limit_cycles : AR_DEFAULT_LIMIT;
     int* err = tc_error_ptr();
     SV_CHECK_ARG(err != nullptr, "svtad_allreduce_sum: no current CUDA device");
+    if (getenv("SVTAD_ALLREDUCE_NO_CARVEOUT") == nullptr) {
+        rc = ar_prefer_shared(reinterpret_cast<const void*>(allreduce_twoshot_kernel));
+        if (rc) return rc;
+    }
     allreduce_twoshot_kernel<<<ar_ctas(n_vec, world), AR_THREADS, 0, (cudaStream_t)stream>>>(
-        peers, rank, world, n_vec, stage_offset_bytes, static_cast<unsigned*>(epoch), dtype == SVTAD_F16 ? 1 : 0, limit, err);
+        peers, rank, world, n_vec, stage_offset_bytes, static_cast<unsigned*>(epoch), dtype == SVTAD_F16 ? 1 : 0, limit, err, ar_backoff());
     SV_LAUNCH_CHECK("allreduce_twoshot_kernel");
     return SVTAD_OK;
 }
@@ -232,8 +278,9 @@ extern "C" int svtad_allreduce_sum_emulated(void* const* bufs, int world, int64_
     int* err = tc_error_ptr();
     SV_CHECK_ARG(err != nullptr, "svtad_allreduce_sum_emulated: no current CUDA device");
     int ctas = ar_ctas(n_vec, world);
-    if (ctas * world > 128) ctas = 128 / world;          // every CTA of every rank must be resident at once (148 SMs)
-    void* args[] = {&peers, &world, &n_vec, &flag_off, &ep, &fp16, &limit, &err};
+    if (ctas * world > 256) ctas = 256 / world;          // every CTA of every rank must be resident at once (148 SMs)
+    unsigned backoff = ar_backoff();
+    void* args[] = {&peers, &world, &n_vec, &flag_off, &ep, &fp16, &limit, &err, &backoff};
     SV_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(allreduce_twoshot_emulated_kernel),
                                         dim3((unsigned)ctas, (unsigned)world), dim3(AR_THREADS), args, 0,
                                         (cudaStream_t)stream));
