@@ -552,6 +552,13 @@ def main():
     h2d = sum(it["scores"].numel() * 4 + it["x"].numel() * 2 + it["gy"].numel() * 2 for it in host_sets[0])
     d2h = sum(2 * it["n"] * C * 2 for it in host_sets[0]) + 3 * (KK * C * C * 4 + C * 4)
     layer_streams = [torch.cuda.Stream(device=dev) for _ in KEEPS]
+    # N > 1: the three layers' fp32 gradients go into ONE bucket that is summed once per step on a stream of its own
+    # (high priority, after the three layers' backward) and leaves for the host in one copy
+    e2e_bucket = e2e_comm = grads_h = None
+    if world > 1:
+        e2e_bucket = GradBucket(len(KEEPS) * per_layer, torch.float32, dev)
+        e2e_comm = torch.cuda.Stream(device=dev, priority=-1)
+        grads_h = [torch.empty(len(KEEPS) * per_layer, dtype=torch.float32).pin_memory() for _ in range(N_SETS)]
 
     def e2e_body(si):
         """One step's public-API calls, layer ki on layer_streams[ki]; results land in out_h[si % N_SETS]."""
@@ -567,14 +574,21 @@ def main():
                 with torch.autocast("cuda", dtype=torch.bfloat16):
                     y = module(x, table, local_indices=False)   # tables of the builder hold global row numbers
                 y.backward(gy)
-                if world > 1:
-                    gw_r, gb_r = allreduce_weight_grads(module.weight.grad, module.bias.grad)
-                    module.weight.grad, module.bias.grad = gw_r, gb_r
                 o = out_h[slot][ki]
                 o["y"].copy_(y, non_blocking=True)
                 o["gx"].copy_(x.grad, non_blocking=True)
-                o["gw"].copy_(module.weight.grad, non_blocking=True)
-                o["gb"].copy_(module.bias.grad, non_blocking=True)
+                if world > 1:
+                    e2e_bucket.view(ki * per_layer, (KK, C, C)).copy_(module.weight.grad)
+                    e2e_bucket.view(ki * per_layer + KK * C * C, (C,)).copy_(module.bias.grad)
+                else:
+                    o["gw"].copy_(module.weight.grad, non_blocking=True)
+                    o["gb"].copy_(module.bias.grad, non_blocking=True)
+        if world > 1:
+            for st in layer_streams:
+                e2e_comm.wait_stream(st)
+            with torch.cuda.stream(e2e_comm):
+                e2e_bucket.all_reduce()
+                grads_h[slot].copy_(e2e_bucket.buffer, non_blocking=True)
 
     def fork_join(si):
         """e2e_body between a fork from and a join back to the current stream."""
@@ -584,6 +598,8 @@ def main():
         e2e_body(si)
         for st in layer_streams:
             cur.wait_stream(st)
+        if e2e_comm is not None:
+            cur.wait_stream(e2e_comm)
 
     # Steps alternate between two streams, so the copies in of one step overlap the copies out of the one before
     # (with N > 1 a single stream keeps the ranks' collectives in one order).
