@@ -39,6 +39,8 @@ SIGNATURES = {
     "svtad_allreduce_sum_emulated": (c_int, [ctypes.POINTER(c_p), c_int, c_i64, c_int, c_sz, c_p, c_i64, c_p]),
     "svtad_ffma_probe": (c_int, [c_int, c_int, c_p, c_p]),
     "svtad_device_error": (c_int, [ctypes.POINTER(ctypes.c_int32)]),
+    "svtad_set_concurrency": (c_int, [c_int]),
+    "svtad_get_concurrency": (c_int, []),
     "svtad_path_for": (c_int, [c_int, c_i64, c_int, c_int, c_int, c_int]),
 }
 

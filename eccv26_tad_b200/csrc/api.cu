@@ -84,6 +84,10 @@ extern "C" int svtad_path_for(int op, int64_t n, int cin, int cout, int kk, int 
     return use_tc(op, n, cin, cout, kk, dtype) ? 1 : 0;
 }
 
+extern "C" int svtad_set_concurrency(int kernels) { return tc_set_share(kernels); }
+
+extern "C" int svtad_get_concurrency(void) { return tc_get_share(); }
+
 extern "C" int svtad_device_error(int32_t* code_out) {
     SV_CHECK_ARG(code_out != nullptr, "svtad_device_error: code_out is null");
     return tc_read_error(code_out);
@@ -209,6 +213,12 @@ extern "C" int svtad_conv_bwd(const void* gy, const void* x, const int32_t* nbr,
     std::lock_guard<std::mutex> hold(lane.mu);
     int rc = lane_ready(lane);
     if (rc) return rc;
+    // the two kernels share the GPU: each is planned for half of it unless the caller's hint already says more
+    struct FloorGuard {
+        int old;
+        FloorGuard() : old(tc_set_share_floor(2)) {}
+        ~FloorGuard() { tc_set_share_floor(old); }
+    } floor_guard;
     // fork: the side stream starts where the caller's stream stands
     SV_CUDA(cudaEventRecord(lane.fork, s));
     SV_CUDA(cudaStreamWaitEvent(lane.stream, lane.fork, 0));

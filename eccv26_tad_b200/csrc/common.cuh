@@ -72,6 +72,9 @@ int tc_wgrad(const void* gy, const void* x, const int32_t* nbr, void* gw, void* 
              cudaStream_t s);
 size_t tc_wgrad_ws_bytes(int64_t n, int cin, int cout, int kk);
 int tc_read_error(int32_t* code_out);
+int tc_set_share(int n);
+int tc_get_share();
+int tc_set_share_floor(int n);
 
 // the single-CTA tensor-core kernels behind tc_* (conv_tc_hybrid.cu)
 #define SV_DECLARE_TC_FAMILY(prefix)                                                                        \

@@ -6,6 +6,7 @@
 // reduce kernel) and the atomic backward kernels opentad/models/bricks/2d_sparse_v3.cu:656-745.
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <utility>
@@ -53,6 +54,39 @@ int tc_num_sms() {
     if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
     if (dev >= 0 && dev < MAX_DEV) cached[dev] = v;
     return v;
+}
+
+// How many kernels the caller expects to share the GPU (svtad_set_concurrency; SVTAD_CONCURRENCY for a start value).
+// The planning below then counts on SMs / share multiprocessors per kernel: fewer, longer CTAs (wide column blocks,
+// several row tiles per persistent CTA, fewer token splits), which costs a kernel latency when it runs alone but
+// saves SM time - every CTA pays about 7 us of set-up, first-operand latency and epilogue whatever its share of the
+// work - when the SMs are contended anyway.
+static std::atomic<int>& tc_share_ref() {
+    static std::atomic<int> v{[] {
+        const char* e = getenv("SVTAD_CONCURRENCY");
+        int x = (e != nullptr && *e) ? atoi(e) : 1;
+        return x < 1 ? 1 : (x > 16 ? 16 : x);
+    }()};
+    return v;
+}
+int tc_set_share(int n) {
+    if (n < 1) n = 1;
+    if (n > 16) n = 16;
+    return tc_share_ref().exchange(n);
+}
+int tc_get_share() { return tc_share_ref().load(); }
+// a lower bound on the share for the calling thread's next launches (svtad_conv_bwd runs its two kernels side by
+// side and plans each for half the GPU even when the caller gave no hint)
+static thread_local int t_share_floor = 1;
+int tc_set_share_floor(int n) {
+    const int old = t_share_floor;
+    t_share_floor = n < 1 ? 1 : n;
+    return old;
+}
+int tc_plan_sms() {
+    const int g = tc_share_ref().load();
+    int v = tc_num_sms() / (g > t_share_floor ? g : t_share_floor);
+    return v < 8 ? 8 : v;
 }
 
 // cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel, device) instead of before every launch;
@@ -147,7 +181,7 @@ int tc_pick_bn(int cn, long m_tiles) {
         for (int c : cand)
             if (v == c && cn % v == 0) return v;
     }
-    const long sms = tc_num_sms();
+    const long sms = tc_plan_sms();
     int best = 0;
     long best_cost = 0;
     for (int c : cand) {
@@ -167,7 +201,7 @@ int tc_pick_bn(int cn, long m_tiles) {
 // Cycles per step and the partials' rate are what these kernels were measured at on a B200.
 WgradPlan tc_wgrad_plan(int64_t n, int cin, int cout, int kk) {
     const int nblocks = kk * (cin / 64);
-    const long sms = tc_num_sms();
+    const long sms = tc_plan_sms();
     long max_by_rows = (n + 2 * STAGE_K - 1) / (2 * STAGE_K);
     if (max_by_rows < 1) max_by_rows = 1;
     if (max_by_rows > 64) max_by_rows = 64;

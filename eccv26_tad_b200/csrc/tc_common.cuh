@@ -272,6 +272,10 @@ inline cudaError_t tc_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size
 }
 constexpr size_t TC_SMEM_LIMIT = 227 * 1024;
 int tc_num_sms();
+int tc_plan_sms();          // SMs a kernel is planned for: all of them divided by the caller's concurrency hint
+int tc_set_share(int n);    // sets the hint, returns the previous one
+int tc_get_share();
+int tc_set_share_floor(int n);   // per calling thread; returns the previous floor
 int tc_ensure_smem(const void* kern, size_t bytes);
 // 16-bit tensor map with 128-byte swizzle and zero fill outside the tensor; dims[0] is the contiguous one
 int tc_make_map(CUtensorMap* map, int rank, const void* base, const uint64_t* dims, const uint32_t* box, int fp16);

@@ -353,3 +353,15 @@ def device_error():
 
 def path_for(op, n, cin, cout, kk, dtype):
     return "tc" if _lib.load().svtad_path_for(op, n, cin, cout, kk, _DTYPES[dtype]) else "simt"
+
+
+def set_concurrency(kernels):
+    """How many of the library's kernels the caller expects to share the GPU at a time (independent layers on their
+    own streams, forward next to backward).  1 (default) plans every kernel for the whole GPU - best for a kernel
+    that runs alone; k > 1 plans for ``SMs / k``: fewer, longer CTAs that cost a lone kernel latency and save SM time
+    under contention.  Process-wide; returns the previous value.  See ``svtad_set_concurrency`` in ``svtad.h``."""
+    return int(_lib.load().svtad_set_concurrency(int(kernels)))
+
+
+def get_concurrency():
+    return int(_lib.load().svtad_get_concurrency())

@@ -217,6 +217,24 @@ int svtad_allreduce_sum_emulated(void* const* bufs, int world, int64_t n_elems, 
                                  size_t stage_offset_bytes, void* epochs, int64_t wait_limit_cycles, void* stream);
 
 /*
+ * Concurrency hint (no counterpart in the reference): how many of this library's kernels the caller expects to
+ * share the GPU at a time - independent layers on streams of their own, forward next to backward.  The default, 1,
+ * plans every kernel for the whole GPU, which gives a kernel that runs alone its shortest latency.  With a hint of
+ * k the tensor-core kernels are planned for (SMs / k) multiprocessors each: wide column blocks, persistent CTAs
+ * that take several row tiles in turn, fewer token splits in the weight gradient.  Every CTA pays a few
+ * microseconds of set-up, first-operand latency and epilogue whatever its share of the work, so fewer and longer
+ * CTAs cost a lone kernel latency but save SM time when the SMs are contended anyway (three layers' passes in one
+ * step on a B200: 0.110 ms with the default, 0.086 ms with a hint of 3).  Results do not depend on the hint beyond
+ * the summation order of the weight gradient's partials.  The hint is process-wide and read at launch time; set it
+ * before sizing workspaces with svtad_workspace_bytes (a larger hint never needs more).  svtad_conv_bwd, whose two
+ * kernels run side by side, plans them for half the GPU each even under the default.
+ * svtad_set_concurrency returns the previous value (values are clamped to [1, 16]); SVTAD_CONCURRENCY in the
+ * environment gives the start value.
+ */
+int svtad_set_concurrency(int kernels);
+int svtad_get_concurrency(void);
+
+/*
  * Reads (and clears) the device-side error word of the current device: non-zero means a bounded
  * wait inside a kernel gave up and that launch's output is invalid.  Synchronises
  * the device.  No reference counterpart.

@@ -87,6 +87,36 @@ def test_config2_bf16_fwd_bwd_full_size(keep, path, monkeypatch):
     _check_all(table, x, w, b, gy, outs, 2e-2)
 
 
+@pytest.mark.parametrize("hint", [2, 3, 6])
+@pytest.mark.parametrize("keep", [0.10, 0.30, 0.55])
+def test_concurrency_hint_changes_the_plans_not_the_results(hint, keep):
+    """svtad_set_concurrency(k) plans the tensor-core kernels for a k-th of the GPU: wide column blocks, persistent
+    CTAs that take several row tiles in turn, fewer token splits.  Forward and input gradient must come out bit for
+    bit as under the default (their summation order does not depend on the plan); the weight gradient's partials
+    are summed in another order, so it is held to the oracle and to the default's result within rounding."""
+    ops = _ops()
+    _, _, table = make_table(2, 80, 14, 14, keep, 3, BASE_SEED + 2)
+    n = table.shape[0]
+    x, w, b, gy = make_conv_inputs(n, 192, 192, 3, torch.bfloat16, BASE_SEED + 2, bias="random")
+    assert ops.get_concurrency() == 1
+    base = _run_all(table, x, w, b, gy)
+    prev = ops.set_concurrency(hint)
+    try:
+        assert prev == 1 and ops.get_concurrency() == hint
+        outs = _run_all(table, x, w, b, gy)
+        tc_, xc, wc, gc = (t.cuda() for t in (table, x, w, gy))
+        gx2, gw2, gb2 = ops.conv_bwd(gc, xc, tc_, wc, assume_symmetric=True)      # the one-call backward under the hint
+        torch.cuda.synchronize()
+    finally:
+        ops.set_concurrency(1)
+    assert torch.equal(outs[0], base[0]) and torch.equal(outs[1], base[1])
+    assert torch.equal(gx2, base[1])
+    _check_all(table, x, w, b, gy, outs, 2e-2)
+    for a, r in ((outs[2], base[2]), (outs[3], base[3]), (gw2, base[2]), (gb2, base[3])):
+        assert oconv.rel_err(f32np(a), f32np(r).astype(np.float64)) < 1e-2
+    assert ops.device_error() == 0
+
+
 @pytest.mark.parametrize("bn", ["64", "96", "192"])
 def test_tc_column_block_variants(bn, monkeypatch):
     monkeypatch.setenv("SVTAD_FORCE_PATH", "tc")
@@ -375,7 +405,16 @@ def test_one_call_backward_equals_the_two_halves(dtype, C, kind, monkeypatch):
     x, w, b, gy = make_conv_inputs(n, C, C, 3, dtype, 33)
     tc, xc, wc, gc = (t.cuda() for t in (table, x, w, gy))
     gx0 = ops.conv_dgrad(gc, tc, wc)
-    gw0, gb0 = ops.conv_wgrad(gc, xc, tc, 9)
+    gw_alone, gb_alone = ops.conv_wgrad(gc, xc, tc, 9)
+    # when both gradients are asked for, the call plans its two side-by-side kernels for half the GPU each: the same
+    # plan (and so the same summation order of the weight gradient's partials) as the halves under a hint of 2
+    ops.set_concurrency(2)
+    try:
+        gw0, gb0 = ops.conv_wgrad(gc, xc, tc, 9)
+        assert torch.equal(ops.conv_dgrad(gc, tc, wc), gx0) or kind != "geometric"
+    finally:
+        ops.set_concurrency(1)
+    assert oconv.rel_err(f32np(gw0), f32np(gw_alone).astype(np.float64)) < 1e-2
 
     def same_gx(a):
         if kind == "geometric":
@@ -388,8 +427,8 @@ def test_one_call_backward_equals_the_two_halves(dtype, C, kind, monkeypatch):
         assert same_gx(gx) and torch.equal(gw, gw0) and torch.equal(gb, gb0)
     gx, gw, gb = ops.conv_bwd(gc, xc, tc, wc, need_w=False, need_b=False)
     assert gw is None and gb is None and same_gx(gx)
-    gx, gw, gb = ops.conv_bwd(gc, xc, tc, wc, need_x=False)
-    assert gx is None and torch.equal(gw, gw0) and torch.equal(gb, gb0)
+    gx, gw, gb = ops.conv_bwd(gc, xc, tc, wc, need_x=False)       # one kernel: planned alone
+    assert gx is None and torch.equal(gw, gw_alone) and torch.equal(gb, gb_alone)
     gx, gw, gb = ops.conv_bwd(gc, xc, tc, wc, need_b=False)
     assert gb is None and same_gx(gx) and torch.equal(gw, gw0)
     # the caller's stream alone orders the results: consume them at once on a non-default stream

@@ -211,3 +211,15 @@ def test_top_level_opentad_sparse_ops_module():
         assert getattr(mod, name) is getattr(shim, name)
     text = open(os.path.join(ROOT, "setup.py")).read()
     assert 'py_modules=["opentad_sparse_ops"]' in text and "libsvtad.so" in text
+
+
+def test_concurrency_hint_round_trip_and_clamping():
+    """The hint is host state of the library: settable and readable without a GPU, clamped to [1, 16]."""
+    lib = _lib.load()
+    start = lib.svtad_get_concurrency()
+    try:
+        assert lib.svtad_set_concurrency(3) == start and lib.svtad_get_concurrency() == 3
+        assert lib.svtad_set_concurrency(0) == 3 and lib.svtad_get_concurrency() == 1
+        assert lib.svtad_set_concurrency(99) == 1 and lib.svtad_get_concurrency() == 16
+    finally:
+        lib.svtad_set_concurrency(start)
