@@ -235,9 +235,10 @@ def main():
     ap.add_argument("--layer-streams", type=int, default=1, choices=[0, 1],
                     help="1 (default): the step's three layers (keep rates), which do not depend on one another, run on "
                          "three streams; 0: one after the other")
-    ap.add_argument("--concurrency", type=int, default=3,
-                    help="svtad_set_concurrency hint for the step (its three layers run on streams of their own); "
-                         "1 plans every kernel for the whole GPU")
+    ap.add_argument("--concurrency", default="3,2,2",
+                    help="svtad_set_concurrency hints for the step, one per layer in the order of the keep rates (the "
+                         "three layers run on streams of their own; the layers that carry more of the work are planned "
+                         "for a larger share of the GPU), or one number for all; 1 plans every kernel for the whole GPU")
     ap.add_argument("--ar-per-layer", type=int, default=0, choices=[0, 1],
                     help="N > 1: 1 = one gradient bucket per layer, exchanged while the other layers still compute")
     ap.add_argument("--skip-cpu", action="store_true")
@@ -358,6 +359,7 @@ def main():
             early_wgrad = True
 
         def wgrad(li, it, st):
+            ops.set_concurrency(layer_hints[li])
             ops._lib.check(lib.svtad_conv_wgrad(it["gy"].data_ptr(), it["x"].data_ptr(), it["table"].data_ptr(),
                                                 gw_bufs[li].data_ptr(), gb_bufs[li].data_ptr(), it["n"], C, C, KK, 0, code,
                                                 ws_l[li].data_ptr(), ws_bytes, st.cuda_stream))
@@ -376,6 +378,7 @@ def main():
             side = sides[li]
             if args.layer_streams:
                 main.wait_stream(cur)
+            ops.set_concurrency(layer_hints[li])
             ops._lib.check(lib.svtad_conv_fwd(it["x"].data_ptr(), it["table"].data_ptr(), weight.data_ptr(),
                                               bias.data_ptr(), y_bufs[li].data_ptr(), n, C, C, KK, 0, code, None, 0,
                                               main.cuda_stream))
@@ -401,11 +404,17 @@ def main():
         elif world > 1:
             buckets[0].all_reduce()
             nl += 1
+        ops.set_concurrency(hint)
         return nl
 
     # The three layers of a step run side by side, so the kernels are planned for a share of the GPU each
     # (svtad_set_concurrency; workspaces were sized under the default, which never needs less).
-    hint = max(1, args.concurrency) if args.layer_streams else 1
+    layer_hints = [max(1, int(v)) for v in str(args.concurrency).split(",")]
+    if len(layer_hints) == 1:
+        layer_hints = layer_hints * len(KEEPS)
+    if len(layer_hints) != len(KEEPS) or not args.layer_streams:
+        layer_hints = [1] * len(KEEPS)
+    hint = max(layer_hints)            # what stays set outside the step's own calls (the e2e part runs under it)
     ops.set_concurrency(hint)
     stream = torch.cuda.Stream(device=dev)
     graphs = None
@@ -527,14 +536,14 @@ def main():
                             for (name, ki), v in per_kernel.items()},
         "whole_step_frac": 3 * dom_flops / (ms_total / args.steps * 1e-3) / 1e12 / peak_tf,
         "planning": f"the per-launch figures time each kernel alone, planned for the whole GPU (svtad_set_concurrency(1)); "
-                    f"inside the step the kernels are planned with svtad_set_concurrency({hint}) and overlap, "
+                    f"inside the step the kernels of the three layers are planned with svtad_set_concurrency({layer_hints}) and overlap, "
                     f"whole_step_frac is their aggregate",
     }
 
     if os.environ.get("SVTAD_BENCH_VALUE_ONLY"):       # a short line for sweeps: the resident step only
         if rank == 0:
             print(json.dumps({"n_gpus": world, "ms_per_step": ms_total / args.steps, "sweep_line": True,
-                              "run": {"allreduce": allreduce_kind, "concurrency_hint": hint}}))
+                              "run": {"allreduce": allreduce_kind, "concurrency_hints": layer_hints}}))
             sys.stdout.flush()
         if world > 1:
             torch.cuda.synchronize()
@@ -759,7 +768,7 @@ def main():
             "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(world),           # the same dictionary in both arms
-            "run": dict(launch="cuda_graph" if graphs is not None else "eager", concurrency_hint=hint,
+            "run": dict(launch="cuda_graph" if graphs is not None else "eager", concurrency_hints=layer_hints,
                         layer_streams=bool(args.layer_streams), **({"allreduce": allreduce_kind} if world > 1 else {})),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
