@@ -239,6 +239,9 @@ def main():
                     help="svtad_set_concurrency hints for the step, one per layer in the order of the keep rates (the "
                          "three layers run on streams of their own; the layers that carry more of the work are planned "
                          "for a larger share of the GPU), or one number for all; 1 plans every kernel for the whole GPU")
+    ap.add_argument("--wgrad-concurrency", default=None,
+                    help="hints for the weight-gradient kernels if they are to differ from --concurrency "
+                         "(default: 4,3,3 in the N > 1 order, where they are issued first)")
     ap.add_argument("--ar-per-layer", type=int, default=0, choices=[0, 1],
                     help="N > 1: 1 = one gradient bucket per layer, exchanged while the other layers still compute")
     ap.add_argument("--skip-cpu", action="store_true")
@@ -353,26 +356,29 @@ def main():
         runs while the rest of the step still computes."""
         nl = 0
         cur = torch.cuda.current_stream()
-        early_wgrad = (world > 1 and not args.ar_per_layer and args.layer_streams
-                       and os.environ.get("SVTAD_BENCH_EARLY_WGRAD", "1") != "0")
-        if os.environ.get("SVTAD_BENCH_EARLY_WGRAD") == "force":
-            early_wgrad = True
+        early_wgrad = wgrad_first
 
         def wgrad(li, it, st):
-            ops.set_concurrency(layer_hints[li])
+            ops.set_concurrency(wgrad_hints[li])
             ops._lib.check(lib.svtad_conv_wgrad(it["gy"].data_ptr(), it["x"].data_ptr(), it["table"].data_ptr(),
                                                 gw_bufs[li].data_ptr(), gb_bufs[li].data_ptr(), it["n"], C, C, KK, 0, code,
                                                 ws_l[li].data_ptr(), ws_bytes, st.cuda_stream))
 
+        order = list(range(len(dk)))
+        if early_wgrad and os.environ.get("SVTAD_BENCH_BIG_FIRST", "1") == "1":
+            order = order[::-1]          # the layer with the most rows first: its chain is the longest
         if early_wgrad:
-            for li, it in enumerate(dk):
+            for li in order:
+                it = dk[li]
                 sides[li].wait_stream(cur)
                 wgrad(li, it, sides[li])
                 comm.wait_stream(sides[li])
             with torch.cuda.stream(comm):
-                buckets[0].all_reduce()
+                if not os.environ.get("SVTAD_BENCH_NO_EXCHANGE"):       # debugging aid: the step's order without its exchange
+                    buckets[0].all_reduce()
             nl += 1 if world > 1 else 0
-        for li, it in enumerate(dk):
+        for li in order:
+            it = dk[li]
             n = it["n"]
             main = lanes[li] if args.layer_streams else cur
             side = sides[li]
@@ -401,6 +407,15 @@ def main():
                 cur.wait_stream(lanes[li])
         if early_wgrad or (world > 1 and args.ar_per_layer):
             cur.wait_stream(comm)
+        elif world > 1 and args.layer_streams and os.environ.get("SVTAD_BENCH_LATE_EXCHANGE_ON_COMM"):
+            # the N = 1 order (forward, then weight gradient beside input gradient); the exchange follows the weight
+            # gradients on its own stream and overlaps what is left of the input gradients
+            for side in sides:
+                comm.wait_stream(side)
+            with torch.cuda.stream(comm):
+                buckets[0].all_reduce()
+            cur.wait_stream(comm)
+            nl += 1
         elif world > 1:
             buckets[0].all_reduce()
             nl += 1
@@ -414,6 +429,19 @@ def main():
         layer_hints = layer_hints * len(KEEPS)
     if len(layer_hints) != len(KEEPS) or not args.layer_streams:
         layer_hints = [1] * len(KEEPS)
+    # With N > 1 the weight gradients are issued first (see raw_step) and run beside all three forwards: measured
+    # best when they are planned a little leaner than forward / dgrad (0.0782 against 0.0807 ms per step on one GPU
+    # in that order).  In the N = 1 order they share the layer's hint.
+    wgrad_first = (world > 1 and not args.ar_per_layer and bool(args.layer_streams)
+                   and os.environ.get("SVTAD_BENCH_EARLY_WGRAD", "1") != "0") or os.environ.get("SVTAD_BENCH_EARLY_WGRAD") == "force"
+    wgrad_hints = layer_hints
+    wg_arg = args.wgrad_concurrency or ("4,3,3" if wgrad_first and str(args.concurrency) == "3,2,2" else None)
+    if wg_arg and args.layer_streams:
+        wgrad_hints = [max(1, int(v)) for v in str(wg_arg).split(",")]
+        if len(wgrad_hints) == 1:
+            wgrad_hints = wgrad_hints * len(KEEPS)
+        if len(wgrad_hints) != len(KEEPS):
+            wgrad_hints = layer_hints
     hint = max(layer_hints)            # what stays set outside the step's own calls (the e2e part runs under it)
     ops.set_concurrency(hint)
     stream = torch.cuda.Stream(device=dev)
@@ -769,6 +797,7 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(world),           # the same dictionary in both arms
             "run": dict(launch="cuda_graph" if graphs is not None else "eager", concurrency_hints=layer_hints,
+                        wgrad_concurrency_hints=wgrad_hints, order="weight gradients first" if wgrad_first else "forward first",
                         layer_streams=bool(args.layer_streams), **({"allreduce": allreduce_kind} if world > 1 else {})),
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
