@@ -365,7 +365,7 @@ def main():
                                                 ws_l[li].data_ptr(), ws_bytes, st.cuda_stream))
 
         order = list(range(len(dk)))
-        if early_wgrad and os.environ.get("SVTAD_BENCH_BIG_FIRST", "1") == "1":
+        if early_wgrad:
             order = order[::-1]          # the layer with the most rows first: its chain is the longest
         if early_wgrad:
             for li in order:
@@ -374,8 +374,7 @@ def main():
                 wgrad(li, it, sides[li])
                 comm.wait_stream(sides[li])
             with torch.cuda.stream(comm):
-                if not os.environ.get("SVTAD_BENCH_NO_EXCHANGE"):       # debugging aid: the step's order without its exchange
-                    buckets[0].all_reduce()
+                buckets[0].all_reduce()
             nl += 1 if world > 1 else 0
         for li in order:
             it = dk[li]
@@ -407,15 +406,6 @@ def main():
                 cur.wait_stream(lanes[li])
         if early_wgrad or (world > 1 and args.ar_per_layer):
             cur.wait_stream(comm)
-        elif world > 1 and args.layer_streams and os.environ.get("SVTAD_BENCH_LATE_EXCHANGE_ON_COMM"):
-            # the N = 1 order (forward, then weight gradient beside input gradient); the exchange follows the weight
-            # gradients on its own stream and overlaps what is left of the input gradients
-            for side in sides:
-                comm.wait_stream(side)
-            with torch.cuda.stream(comm):
-                buckets[0].all_reduce()
-            cur.wait_stream(comm)
-            nl += 1
         elif world > 1:
             buckets[0].all_reduce()
             nl += 1
@@ -433,7 +423,7 @@ def main():
     # best when they are planned a little leaner than forward / dgrad (0.0782 against 0.0807 ms per step on one GPU
     # in that order).  In the N = 1 order they share the layer's hint.
     wgrad_first = (world > 1 and not args.ar_per_layer and bool(args.layer_streams)
-                   and os.environ.get("SVTAD_BENCH_EARLY_WGRAD", "1") != "0") or os.environ.get("SVTAD_BENCH_EARLY_WGRAD") == "force"
+                   and os.environ.get("SVTAD_BENCH_EARLY_WGRAD", "1") != "0")
     wgrad_hints = layer_hints
     wg_arg = args.wgrad_concurrency or ("4,3,3" if wgrad_first and str(args.concurrency) == "3,2,2" else None)
     if wg_arg and args.layer_streams:

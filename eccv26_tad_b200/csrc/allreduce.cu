@@ -252,10 +252,8 @@ extern "C" int svtad_allreduce_sum(void* const* peer_bufs, int rank, int world, 
     const long long limit = wait_limit_cycles > 0 ? wait_limit_cycles : AR_DEFAULT_LIMIT;
     int* err = tc_error_ptr();
     SV_CHECK_ARG(err != nullptr, "svtad_allreduce_sum: no current CUDA device");
-    if (getenv("SVTAD_ALLREDUCE_NO_CARVEOUT") == nullptr) {
-        rc = ar_prefer_shared(reinterpret_cast<const void*>(allreduce_twoshot_kernel));
-        if (rc) return rc;
-    }
+    rc = ar_prefer_shared(reinterpret_cast<const void*>(allreduce_twoshot_kernel));
+    if (rc) return rc;
     allreduce_twoshot_kernel<<<ar_ctas(n_vec, world), AR_THREADS, 0, (cudaStream_t)stream>>>(
         peers, rank, world, n_vec, stage_offset_bytes, static_cast<unsigned*>(epoch), dtype == SVTAD_F16 ? 1 : 0, limit, err, ar_backoff());
     SV_LAUNCH_CHECK("allreduce_twoshot_kernel");
