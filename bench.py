@@ -534,7 +534,8 @@ def main():
         for name, fn in (("fwd", f_fwd), ("dgrad", f_dg), ("wgrad", f_wg)):
             per_kernel[(name, ki)] = time_op(fn, reps)
     torch.cuda.synchronize()
-    ops.set_concurrency(hint)
+    # the end-to-end part below is bound by the host link, its SMs are mostly idle: every kernel stays planned for the
+    # whole GPU there (shortest latency per layer; measured no different from the step's hints: 0.73-0.75 ms either way)
     totals = {name: sum(per_kernel[(name, ki)] for ki in range(len(KEEPS))) for name in ("fwd", "dgrad", "wgrad")}
     dominant = max(totals, key=totals.get)
     peak_tf, peak_hbm, peak_kind = measured_peaks()
