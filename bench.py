@@ -432,7 +432,7 @@ def main():
             wgrad_hints = wgrad_hints * len(KEEPS)
         if len(wgrad_hints) != len(KEEPS):
             wgrad_hints = layer_hints
-    hint = max(layer_hints)            # what stays set outside the step's own calls (the e2e part runs under it)
+    hint = max(layer_hints)            # what stays set between the step's own calls
     ops.set_concurrency(hint)
     stream = torch.cuda.Stream(device=dev)
     graphs = None
