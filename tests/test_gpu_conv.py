@@ -368,12 +368,23 @@ def test_empty_input_and_all_pruned_rows():
     assert torch.equal(y.cpu(), b.expand(n, -1).contiguous())
 
 
-def test_tensor_core_pipeline_is_race_free(monkeypatch):
+@pytest.mark.parametrize("hint,keep", [(1, 0.3), (3, 0.3), (4, 0.55)])
+def test_tensor_core_pipeline_is_race_free(hint, keep, monkeypatch):
     """The tensor-core kernels are deterministic, so any hazard between the copy engine's writes
-    and the MMA's reads would show as a run-to-run difference.  40 repeats, bitwise equal."""
+    and the MMA's reads would show as a run-to-run difference.  40 repeats, bitwise equal - also with persistent
+    CTAs that take several row tiles in turn (hint 3: 74 tiles on 49 CTAs; hint 4: 135 tiles on 37), where the
+    table rows of the next tile, the two accumulators and the staged bias change hands between tiles."""
     monkeypatch.setenv("SVTAD_FORCE_PATH", "tc")
     ops = _ops()
-    _, _, table = make_table(2, 80, 14, 14, 0.3, 3, 77)
+    request_hint = ops.set_concurrency(hint)
+    try:
+        _race_free_body(ops, keep)
+    finally:
+        ops.set_concurrency(request_hint)
+
+
+def _race_free_body(ops, keep):
+    _, _, table = make_table(2, 80, 14, 14, keep, 3, 77)
     n = table.shape[0]
     x, w, b, gy = make_conv_inputs(n, 192, 192, 3, torch.bfloat16, 77, bias="random")
     tc, xc, wc, bc, gc = (t.cuda() for t in (table, x, w, b, gy))
@@ -388,6 +399,23 @@ def test_tensor_core_pipeline_is_race_free(monkeypatch):
                 assert torch.equal(u, v)
     # and the result is the right one
     assert oconv.rel_err(f32np(first[0]), oconv.fwd(f32np(x), table.numpy(), f32np(w), f32np(b))) < 2e-2
+
+
+@pytest.mark.parametrize("C", [128, 192])
+def test_persistent_ctas_with_a_ragged_last_tile(C):
+    """Hint 16 leaves 9 CTAs for 21 row tiles, the last of them 37 rows: every CTA walks two or three tiles and one
+    of them meets the ragged end.  Against the full oracle, bias on."""
+    ops = _ops()
+    n = 128 * 20 + 37
+    table = _chain_table(n)
+    x, w, b, gy = make_conv_inputs(n, C, C, 3, torch.bfloat16, 5, bias="random")
+    ops.set_concurrency(16)
+    try:
+        outs = _run_all(table, x, w, b, gy, sym=True)
+    finally:
+        ops.set_concurrency(1)
+    _check_all(table, x, w, b, gy, outs, 2e-2)
+    assert ops.device_error() == 0
 
 
 @pytest.mark.parametrize("dtype,C,kind", [(torch.bfloat16, 192, "geometric"), (torch.float32, 32, "geometric"),
