@@ -205,7 +205,11 @@ int svtad_conv_wgrad_static(const void* gy, const void* x, const int32_t* nbr, v
  *               runs out the CTA records code 71 / 72 in the device error word (svtad_device_error), leaves the
  *               bucket as it is and returns; nothing hangs and the context stays usable.
  * Every rank must make the same sequence of calls.  The launch can be captured into a CUDA graph (the call
- * number that the flags carry is kept on the device).  No multicast, no NVLS.
+ * number that the flags carry is kept on the device).  No multicast, no NVLS.  The kernel is built to run beside
+ * the convolution kernels: up to 128 CTAs (SVTAD_ALLREDUCE_CTAS) of 128 threads, no dynamic shared memory, the
+ * same shared-memory / L1 split as the convolution kernels, so its CTAs fit into what a convolution CTA leaves
+ * free on an SM.  To hide it behind other work, put it (and the weight gradients it waits for) on a stream of
+ * higher priority than the rest.
  * svtad_allreduce_sum_emulated runs all ranks' parts in one cooperative launch on the current device (`bufs` are
  * then `world` local buffers, `epochs` holds svtad_allreduce_epoch_bytes()): for tests on machines with fewer GPUs than ranks.
  */
