@@ -413,7 +413,7 @@ def main():
         return nl
 
     # The three layers of a step run side by side, so the kernels are planned for a share of the GPU each
-    # (svtad_set_concurrency; workspaces were sized under the default, which never needs less).
+    # (svtad_set_concurrency; workspace sizes do not depend on the hint).
     layer_hints = [max(1, int(v)) for v in str(args.concurrency).split(",")]
     if len(layer_hints) == 1:
         layer_hints = layer_hints * len(KEEPS)

@@ -199,9 +199,8 @@ int tc_pick_bn(int cn, long m_tiles) {
 //   (waves over the SMs) x (64-token steps per CTA + fixed cost) x (cycles per step at that BN)
 // plus the trip of the fp32 partials through memory (written by the main kernel, read by the reduction).
 // Cycles per step and the partials' rate are what these kernels were measured at on a B200.
-WgradPlan tc_wgrad_plan(int64_t n, int cin, int cout, int kk) {
+static WgradPlan wgrad_plan_for(int64_t n, int cin, int cout, int kk, long sms) {
     const int nblocks = kk * (cin / 64);
-    const long sms = tc_plan_sms();
     long max_by_rows = (n + 2 * STAGE_K - 1) / (2 * STAGE_K);
     if (max_by_rows < 1) max_by_rows = 1;
     if (max_by_rows > 64) max_by_rows = 64;
@@ -247,6 +246,8 @@ WgradPlan tc_wgrad_plan(int64_t n, int cin, int cout, int kk) {
     return best;
 }
 
+WgradPlan tc_wgrad_plan(int64_t n, int cin, int cout, int kk) { return wgrad_plan_for(n, cin, cout, kk, tc_plan_sms()); }
+
 static size_t plan_bytes(const WgradPlan& pl, int64_t n, int cin, int cout, int kk) {
     size_t w = (size_t)pl.splits * kk * cin * cout * sizeof(float);
     int sb = pl.ones_block ? pl.splits : bias_splits_for(n);
@@ -254,11 +255,26 @@ static size_t plan_bytes(const WgradPlan& pl, int64_t n, int cin, int cout, int 
     return align_up(w, 256) + align_up(b, 256);
 }
 
+// Workspace of the plan in force at this moment (what a launch checks its workspace against) ...
 size_t tc_wgrad_plan_ws_bytes(int64_t n, int cin, int cout, int kk) {
     return plan_bytes(tc_wgrad_plan(n, cin, cout, kk), n, cin, cout, kk);
 }
 
-size_t tc_wgrad_ws_bytes(int64_t n, int cin, int cout, int kk) { return tc_wgrad_plan_ws_bytes(n, cin, cout, kk); }
+// ... and what callers are told to provide: enough for the plan under every concurrency hint, so that a workspace
+// sized once stays valid when the hint changes (a leaner plan usually has fewer token splits, but the waves'
+// rounding can go the other way: 18 880 rows at C=192, 5x5 takes 3 splits planned for 148 SMs and 5 for 74).
+size_t tc_wgrad_ws_bytes(int64_t n, int cin, int cout, int kk) {
+    size_t need = 0;
+    const int sms = tc_num_sms();
+    for (int share = 1; share <= 16; ++share) {
+        int v = sms / share;
+        if (v < 8) v = 8;
+        const size_t b = plan_bytes(wgrad_plan_for(n, cin, cout, kk, v), n, cin, cout, kk);
+        if (b > need) need = b;
+    }
+    return need;
+}
+
 
 // fixed-order reduction of the per-split partials (4 elements per thread), one rounding
 __global__ void __launch_bounds__(256)

@@ -229,8 +229,9 @@ int svtad_allreduce_sum_emulated(void* const* bufs, int world, int64_t n_elems, 
  * microseconds of set-up, first-operand latency and epilogue whatever its share of the work, so fewer and longer
  * CTAs cost a lone kernel latency but save SM time when the SMs are contended anyway (three layers' passes in one
  * step on a B200: 0.110 ms with the default, 0.086 ms with a hint of 3).  Results do not depend on the hint beyond
- * the summation order of the weight gradient's partials.  The hint is process-wide and read at launch time; set it
- * before sizing workspaces with svtad_workspace_bytes (a larger hint never needs more).  svtad_conv_bwd, whose two
+ * the summation order of the weight gradient's partials.  The hint is process-wide and read at launch time;
+ * svtad_workspace_bytes does not depend on it (it covers the plan under every hint), so a workspace sized once
+ * stays valid when the hint changes.  svtad_conv_bwd, whose two
  * kernels run side by side, plans them for half the GPU each even under the default.
  * svtad_set_concurrency returns the previous value (values are clamped to [1, 16]); SVTAD_CONCURRENCY in the
  * environment gives the start value.

@@ -471,6 +471,21 @@ def test_one_call_backward_equals_the_two_halves(dtype, C, kind, monkeypatch):
     assert torch.equal(sums[:1], ref[:1]) if kind == "geometric" else abs(float(sums[0] - ref[0])) <= 1e-2 * float(gx0.float().abs().sum())
 
 
+def test_one_call_backward_where_the_half_gpu_plan_needs_more_splits():
+    """18 880 rows, C=192, 5x5: the weight gradient planned for half the GPU (as the one-call backward does) takes
+    more token splits than planned for all of it; the workspace that svtad_workspace_bytes asks for must cover both."""
+    ops = _ops()
+    _, _, table = make_table(4, 80, 14, 14, 0.3, 5, BASE_SEED + 3)
+    n = table.shape[0]
+    x, w, b, gy = make_conv_inputs(n, 192, 192, 5, torch.bfloat16, BASE_SEED + 3, bias="random")
+    tc, xc, wc, gc = (t.cuda() for t in (table, x, w, gy))
+    gx, gw, gb = ops.conv_bwd(gc, xc, tc, wc, assume_symmetric=True)
+    y = ops.conv_fwd(xc, tc, wc, b.cuda())
+    torch.cuda.synchronize()
+    _check_sampled(table, x, w, b, gy, (y, gx, gw, gb), 2e-2, row_step=64, n_ci=6)
+    assert ops.device_error() == 0
+
+
 def _fused_bwd(table, x, w, gy, tpb=0):
     ops = _ops()
     tc, xc, wc, gc = (t.cuda() for t in (table, x, w, gy))

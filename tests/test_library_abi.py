@@ -223,3 +223,23 @@ def test_concurrency_hint_round_trip_and_clamping():
         assert lib.svtad_set_concurrency(99) == 1 and lib.svtad_get_concurrency() == 16
     finally:
         lib.svtad_set_concurrency(start)
+
+
+def test_workspace_sizes_do_not_depend_on_the_concurrency_hint():
+    """A workspace sized once must stay valid when the hint changes (svtad_conv_bwd plans its weight gradient for half
+    the GPU whatever the caller's hint): svtad_workspace_bytes covers the plan under every hint."""
+    lib = _lib.load()
+    shapes = [(n, c, kk) for n in (4, 944, 3200, 9440, 17280, 18880, 40000, 226560) for c in (64, 192, 256, 768, 1024)
+              for kk in (9, 25)]
+    start = lib.svtad_get_concurrency()
+    try:
+        lib.svtad_set_concurrency(1)
+        base = {s: [lib.svtad_workspace_bytes(op, s[0], s[1], s[1], s[2], _lib.BF16) for op in (_lib.OP_WGRAD, _lib.OP_BWD)]
+                for s in shapes}
+        for hint in (2, 3, 4, 7, 16):
+            lib.svtad_set_concurrency(hint)
+            for s in shapes:
+                got = [lib.svtad_workspace_bytes(op, s[0], s[1], s[1], s[2], _lib.BF16) for op in (_lib.OP_WGRAD, _lib.OP_BWD)]
+                assert got == base[s], (hint, s)
+    finally:
+        lib.svtad_set_concurrency(start)
