@@ -200,7 +200,10 @@ int svtad_conv_wgrad_static(const void* gy, const void* x, const int32_t* nbr, v
  *   stage_offset_bytes   where, behind the bucket in the same allocation, svtad_allreduce_stage_bytes(n_elems)
  *               bytes of staging space live; they must be zero before the first call and belong to this function
  *               afterwards
- *   epoch       svtad_allreduce_epoch_bytes() bytes of LOCAL device memory, zero before the first call
+ *   epoch       svtad_allreduce_epoch_bytes() bytes of LOCAL device memory, zero before the first call; it holds
+ *               one call counter per CTA, so it (and the staging space) belongs to ONE bucket of one size: the
+ *               launch shape follows from n_elems, and a counter array used with buckets of different sizes
+ *               would let its counters drift apart
  *   wait_limit_cycles   how long a CTA waits for a peer (SM clock cycles; 0 = about one second).  When the limit
  *               runs out the CTA records code 71 / 72 in the device error word (svtad_device_error), leaves the
  *               bucket as it is and returns; nothing hangs and the context stays usable.
